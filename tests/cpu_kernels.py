@@ -80,11 +80,17 @@ class CpuKernels:
         return False  # the stand-in always prepares q and k in a step of their own
 
     def qk_norm_rope_store(self, qkv, num_q, num_kv, D, q_w, k_w, eps, cos, sin, rotary_dim, positions,
-                           slot_mapping, k_pages, v_pages):
+                           slot_mapping, k_pages, v_pages, v_dim=None, kv_in_row=True):
         self._count("qk_norm_rope_store")
         T = qkv.shape[0]
-        x = qkv.float().clone().view(T, num_q + 2 * num_kv, D)
-        q, k, v = x[:, :num_q], x[:, num_q:num_q + num_kv], x[:, num_q + num_kv:]
+        Dv = D if v_dim is None else v_dim
+        x = qkv.float().clone()
+        q = x[:, :num_q * D].reshape(T, num_q, D)
+        if kv_in_row:
+            k = x[:, num_q * D:(num_q + num_kv) * D].reshape(T, num_kv, D)
+            v = x[:, (num_q + num_kv) * D:].reshape(T, num_kv, Dv)
+        else:
+            k, v, slot_mapping = q[:, :0], None, None
 
         def norm(t, w):
             if w is None:
@@ -105,7 +111,7 @@ class CpuKernels:
         qkv[:, : num_q * D] = q.reshape(T, num_q * D).to(qkv.dtype)
         if slot_mapping is not None:
             kf = k_pages.view(-1, num_kv, D)
-            vf = v_pages.view(-1, num_kv, D)
+            vf = v_pages.view(-1, num_kv, Dv)
             sm = slot_mapping[:T].long()
             ok = sm >= 0
             kf[sm[ok]] = k[ok].to(kf.dtype)
@@ -121,14 +127,15 @@ class CpuKernels:
         qkv.copy_(x.view(T, -1).to(qkv.dtype))
 
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req,
-                        num_q, num_kv, D, page_size, window, scale, ctx=None, ragged=False):
+                        num_q, num_kv, D, page_size, window, scale, ctx=None, ragged=False, v_dim=None, keep_first=0):
         self._count("paged_attention")
         T = out.shape[0]
+        Dv = D if v_dim is None else v_dim
         kf = k_pages.view(-1, num_kv, D).float()
-        vf = v_pages.view(-1, num_kv, D).float()
-        q = qkv[:T, : num_q * D].float().view(T, num_q, D)
+        vf = v_pages.view(-1, num_kv, Dv).float()
+        q = qkv[:T, : num_q * D].float().reshape(T, num_q, D)
         group = num_q // num_kv
-        o = torch.zeros(T, num_q, D)
+        o = torch.zeros(T, num_q, Dv)
         for t in range(T):
             r = int(token_req[t])
             if r < 0:
@@ -139,7 +146,7 @@ class CpuKernels:
             if qlen <= 0 or kvl <= 0 or pos < 0:
                 continue
             lo = max(0, pos - window + 1) if window > 0 else 0
-            keys = torch.arange(lo, pos + 1)
+            keys = torch.cat((torch.arange(0, min(keep_first, lo)), torch.arange(lo, pos + 1)))
             pages = block_table[int(req_slots[r])][(keys // page_size).long()].long()
             assert (pages >= 0).all(), "attention touched a page that was given back"
             slots = pages * page_size + keys % page_size
@@ -148,7 +155,127 @@ class CpuKernels:
                 s = (kf[slots, kh] @ q[t, h]) * scale
                 p = torch.softmax(s, 0)
                 o[t, h] = p @ vf[slots, kh]
-        out.copy_(o.reshape(T, num_q * D).to(out.dtype))
+        out.copy_(o.reshape(T, num_q * Dv).to(out.dtype))
+
+    # -- a 32-bit residual stream, matrix memory, routed experts -----------------------------
+    def embed_scaled(self, ids, table, stream, copy=None, scale=1.0, inv_freq=None, positions=None, last_tokens=None,
+                     token_req=None, req_slots=None):
+        self._count("embedding")
+        T, H = stream.shape
+        idx = ids[:T].long().clone()
+        if last_tokens is not None:
+            for t in (idx < 0).nonzero().flatten().tolist():
+                b = int(token_req[t])
+                idx[t] = int(last_tokens[int(req_slots[b])]) if b >= 0 else 0
+        v = table[idx].float() * scale
+        if inv_freq is not None:
+            ang = positions[:T].float()[:, None] * inv_freq[None, :]
+            pe = torch.stack((torch.sin(ang), torch.cos(ang)), -1).reshape(T, -1)[:, :H]
+            v = v + pe
+        stream.copy_(v)
+        if copy is not None:
+            copy.copy_(v.to(copy.dtype))
+
+    def norm_scale_add(self, a, stream, weight, eps, mult, copy=None):
+        self._count("add_rmsnorm")
+        x = a.float()
+        stream += mult * (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight)
+        if copy is not None:
+            copy.copy_(stream.to(copy.dtype))
+
+    def rmsnorm_rows_f32(self, stream, rows, weight, eps, out):
+        self._count("add_rmsnorm")
+        s = stream[: out.shape[0]] if rows is None else stream[rows[: out.shape[0]].long()]
+        out.copy_((s / torch.sqrt(s.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
+
+    def cast_rows_f32(self, src, out):
+        out.copy_(src.to(out.dtype))
+
+    def act_mul_clamped(self, gate_up, out, limit, alpha):
+        self._count("act_mul")
+        I = out.shape[1]
+        g = gate_up[:, :I].float().clamp(max=limit)
+        u = gate_up[:, I:].float().clamp(-limit, limit)
+        out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
+
+    def mlstm_recurrence(self, qkv, q_off, k_off, v_off, gates, bias_i, bias_f, state, cu_q, req_slots, token_req, out,
+                         requests, heads, dim, vdim, q_scale, cap):
+        self._count("mlstm")
+        x = qkv.float()
+        for r in range(requests):
+            t0, t1 = int(cu_q[r]), int(cu_q[r + 1])
+            if t1 <= t0:
+                continue
+            if int(token_req[t0]) < 0:
+                out[t0:t1] = 0
+                continue
+            row = state[int(req_slots[r])]
+            S = row[: heads * vdim * dim].view(heads, vdim, dim)
+            n = row[heads * vdim * dim: heads * vdim * dim + heads * dim].view(heads, dim)
+            m = row[heads * vdim * dim + heads * dim: heads * vdim * dim + heads * dim + heads]
+            for t in range(t0, t1):
+                q = x[t, q_off:q_off + heads * dim].view(heads, dim) * q_scale
+                k = x[t, k_off:k_off + heads * dim].view(heads, dim)
+                v = x[t, v_off:v_off + heads * vdim].view(heads, vdim)
+                ig = cap * torch.tanh((gates[t, :heads] + bias_i) / cap)
+                fg = torch.nn.functional.logsigmoid(cap * torch.tanh((gates[t, heads:] + bias_f) / cap))
+                m_new = torch.maximum(fg + m, ig)
+                keep, take = torch.exp(fg + m - m_new), torch.exp(ig - m_new)
+                S.mul_(keep[:, None, None]).add_(take[:, None, None] * v[:, :, None] * k[:, None, :])
+                n.mul_(keep[:, None]).add_(take[:, None] * k)
+                m.copy_(m_new)
+                den = torch.maximum((n * q).sum(-1).abs(), torch.exp(-m)) + 1e-6
+                out[t] = (torch.einsum("hvd,hd->hv", S, q) / den[:, None]).reshape(-1)
+
+    def mlstm_out_gate(self, o, g, weight, eps, out, heads, vdim):
+        T = o.shape[0]
+        x = o.view(T, heads, vdim)
+        x = (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, -1)
+        out.copy_((x * weight * torch.sigmoid(g.float())).to(out.dtype))
+
+    def moe_route(self, logits, choice, weight, top, softmax_scores=False, renormalize=False):
+        self._count("moe")
+        s = torch.softmax(logits, -1) if softmax_scores else torch.sigmoid(logits)
+        w, c = torch.topk(s, top, dim=-1)
+        if renormalize:
+            w = w / w.sum(-1, keepdim=True)
+        choice.copy_(c.to(torch.int32))
+        weight.copy_(w)
+
+    def moe_arrange(self, choice, pairs, experts, offsets, sorted_pairs, place):
+        c = choice.reshape(-1)[:pairs].long()
+        order = torch.argsort(c, stable=True)
+        sorted_pairs.view(-1)[:pairs] = order.to(torch.int32)
+        place.view(-1)[order] = torch.arange(pairs, dtype=torch.int32)
+        counts = torch.bincount(c, minlength=experts)
+        offsets.view(-1)[0] = 0
+        offsets.view(-1)[1:experts + 1] = torch.cumsum(counts, 0).to(torch.int32)
+
+    def moe_grouped_linear(self, x, weights, offsets, sorted_pairs, pair_weight, out, top, rows_from_pairs, gated, act=0):
+        self._count("moe")
+        off = offsets.view(-1).tolist()
+        sp = sorted_pairs.view(-1)
+        pw = pair_weight.view(-1) if pair_weight is not None else None
+        n_out = out.shape[1]
+        for e in range(weights.shape[0]):
+            for p in range(off[e], off[e + 1]):
+                pair = int(sp[p])
+                row = x[pair // top if rows_from_pairs else p].float()
+                y = weights[e].float() @ row
+                if pw is not None:
+                    y = y * pw[pair]
+                if gated:
+                    g, u = y[:n_out], y[n_out:]
+                    y = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
+                out[p] = y.to(out.dtype)
+
+    def moe_combine(self, rows, place, pair_weight, y, top):
+        T = y.shape[0]
+        pl = place.view(-1)[: T * top].long()
+        v = rows[pl].float()
+        if pair_weight is not None:
+            v = v * pair_weight.view(-1)[: T * top, None]
+        y.copy_(v.view(T, top, -1).sum(1).to(y.dtype))
 
     def argmax(self, logits, out):
         out[: logits.shape[0]] = torch.argmax(logits, -1).to(torch.int32)

@@ -75,16 +75,31 @@ def plan_groups(needs) -> tuple[list[GroupInfo], list[tuple[int, int] | None]]:
     cache it uses (its own or the one it reads), or None."""
     groups: list[GroupInfo] = []
     where: list[tuple[int, int] | None] = []
+    needs = list(needs)
+    # what a cache must retain is what its writer AND every execution that reads it can still reach
+    kept: dict[int, CacheNeed] = {}
+    for i, (need, _state, cache_of) in enumerate(needs):
+        if need is None:
+            continue
+        if cache_of is None:
+            kept[i] = need
+            continue
+        src_need = needs[cache_of][0]
+        if src_need is None or (src_need.num_kv_heads, src_need.head_dim, src_need.v_dim) != (
+                need.num_kv_heads, need.head_dim, need.v_dim):
+            raise ValueError(f"schedule entry {i} cannot read the cache of entry {cache_of}: different geometry")
+        have = kept[cache_of]
+        window = None if (have.window is None or need.window is None) else max(have.window, need.window)
+        kept[cache_of] = CacheNeed(have.num_kv_heads, have.head_dim, window, have.value_dim,
+                                   0 if window is None else max(have.keep_first, need.keep_first))
     for i, (need, _state, cache_of) in enumerate(needs):
         if need is None:
             where.append(None)
             continue
         if cache_of is not None:
-            src_need = needs[cache_of][0]
-            if src_need is None or (src_need.num_kv_heads, src_need.head_dim) != (need.num_kv_heads, need.head_dim):
-                raise ValueError(f"schedule entry {i} cannot read the cache of entry {cache_of}: different geometry")
             where.append(where[cache_of])
             continue
+        need = kept[i]
         for g, info in enumerate(groups):
             if info.need == need:
                 info.executions.append(i)
@@ -145,7 +160,7 @@ class CacheManager:
             for g in self.groups:
                 shape = (len(g.executions), num_pages, page_size, g.need.num_kv_heads, g.need.head_dim)
                 k = torch.empty(shape, dtype=dtype, device=self.device)
-                v = torch.empty(shape, dtype=dtype, device=self.device)
+                v = torch.empty(shape[:-1] + (g.need.v_dim,), dtype=dtype, device=self.device)
                 if poison:
                     k.fill_(float("nan"))
                     v.fill_(float("nan"))
@@ -169,7 +184,7 @@ class CacheManager:
     @staticmethod
     def bytes_per_page(needs, page_size: int, itemsize: int) -> int:
         groups, _ = plan_groups(list(needs))
-        return sum(2 * len(g.executions) * page_size * g.need.num_kv_heads * g.need.head_dim * itemsize
+        return sum(len(g.executions) * page_size * g.need.num_kv_heads * (g.need.head_dim + g.need.v_dim) * itemsize
                    for g in groups)
 
     def num_free_pages(self, group: int = 0) -> int:
@@ -270,9 +285,10 @@ class CacheManager:
             w = info.need.window
             if w is None:
                 continue
-            # the next token sits at position num_tokens and sees positions >= num_tokens - w + 1
+            # the next token sits at position num_tokens and sees positions >= num_tokens - w + 1, and the first
+            # keep_first positions for ever: the pages that hold those are never given back
             first_needed = max(0, rc.num_tokens - w + 1) // ps
-            lo = rc.first_live_page[g]
+            lo = max(rc.first_live_page[g], -(-info.need.keep_first // ps))
             if first_needed > lo:
                 gone = [p for p in rc.pages[g][lo:first_needed] if p >= 0]
                 self.allocators[g].free(gone)

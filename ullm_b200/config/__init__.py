@@ -1,4 +1,5 @@
 from .engine_config import EngineConfig
+from .ludalix import LudalixConfig, LudalixConfigError, ludalix_model_spec
 from .qwen3 import ConfigError, Qwen3Config, qwen3_model_spec
 from .registry import (
     ARCHITECTURES,
@@ -19,10 +20,11 @@ from .specs import (
 )
 
 register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, qwen3_model_spec)
+register_architecture("Ludalix", LudalixConfig.from_dict, ludalix_model_spec)
 
 __all__ = [
     "ARCHITECTURES", "Architecture", "ConfigError", "EngineConfig", "FeedForwardSpec", "LayerSpec",
-    "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec", "Qwen3Config", "ScheduleEntry",
+    "LudalixConfig", "LudalixConfigError", "ludalix_model_spec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec", "Qwen3Config", "ScheduleEntry",
     "load_model_spec", "qwen3_model_spec", "read_config_json", "register_architecture",
     "resolve_architecture",
 ]

@@ -34,7 +34,8 @@ def register_architecture(name: str, parse_config, model_spec) -> Architecture:
 
 
 def resolve_architecture(config: dict[str, Any]) -> Architecture:
-    names = config.get("architectures") or []
+    # "architectures" (a list, as Hugging Face writes it) or "architecture" (one name)
+    names = config.get("architectures") or config.get("architecture") or []
     if isinstance(names, str):
         names = [names]
     for n in names:

@@ -15,9 +15,13 @@ from typing import Any
 
 @dataclass(frozen=True)
 class NormSpec:
+    """`args`: further keyword arguments of the norm's constructor (the name its weight has in the checkpoint,
+    say)."""
+
     kind: str  # key in parts.registry.NORMS
     size: int
     eps: float
+    args: dict[str, Any] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(frozen=True)
@@ -55,10 +59,12 @@ class LayerSpec:
 
     block: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: FeedForwardSpec | None  # None: the layer has no feed-forward (and no norm for it)
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: NormSpec | None
     names: dict[str, str] = field(default_factory=dict, hash=False, compare=False)
+    # further keyword arguments of the block's constructor (a residual multiplier, say)
+    block_args: dict[str, Any] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(frozen=True)
@@ -88,6 +94,15 @@ class ModelSpec:
     final_norm_name: str = "model.norm."
     head_name: str = "lm_head."
     eos_token_id: int | None = None
+    # the name of the table inside the embedding's and the head's prefix
+    embedding_param: str = "weight"
+    head_param: str = "weight"
+    # x0 = table[id] * embedding_scale (+ an absolute position encoding that is added to the embedding)
+    embedding_scale: float = 1.0
+    embedding_position: PositionSpec | None = None
+    # "engine": the residual stream has the engine's dtype; "float32": it is kept in 32-bit whatever the engine's
+    # dtype (the blocks of such a model take and return a 32-bit stream)
+    stream_dtype: str = "engine"
 
     def validate(self) -> None:
         if not self.layers:

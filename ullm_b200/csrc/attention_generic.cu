@@ -15,7 +15,11 @@
 //
 // Batch row r reads row req_slots[r] of the block table.  Request r owns query rows cu_q[r] .. cu_q[r+1]-1 and holds kv_len[r] tokens
 // after this step; row j of it sits at position kv_len[r] - q_len[r] + j and
-// sees positions max(0, pos - window + 1) .. pos (window 0 = all).
+// sees positions max(0, pos - window + 1) .. pos (window 0 = all), and with
+// `keep_first` > 0 also the positions below keep_first that the window has
+// left behind (they are visited first, in groups of 32 of their own).
+// Values may have a head size of their own (`v_dim`): the value pages are
+// [*, page, kv heads, v_dim] and the output rows [heads, v_dim].
 #include "common.cuh"
 
 #define ATT_MAX_HEAD_DIM 512
@@ -30,7 +34,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
                                                const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                                const int* __restrict__ token_req, int tokens, int num_q, int num_kv,
                                                int head_dim, int page_size, int window, float scale,
-                                               long long num_pages, int* status) {
+                                               long long num_pages, int* status, int v_dim, int keep_first) {
   __shared__ float qs[ATT_WARPS][ATT_MAX_HEAD_DIM];
   pdl_launch_dependents();
   pdl_wait();
@@ -40,13 +44,13 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
   const int t = (int)(unit / num_q);
   const int h = (int)(unit - (long long)t * num_q);
   const int kh = h / (num_q / num_kv);
-  T* o_ptr = out + ((long long)t * num_q + h) * head_dim;
+  T* o_ptr = out + ((long long)t * num_q + h) * v_dim;
   const int r = token_req[t];
   const int q_len = r >= 0 ? cu_q[r + 1] - cu_q[r] : 0;
   const int kvl = r >= 0 ? kv_len[r] : 0;
   const int pos = kvl - q_len + (r >= 0 ? t - cu_q[r] : 0);
   if (r < 0 || q_len <= 0 || kvl <= 0 || pos < 0) {  // padding row
-    for (int e = lane; e < head_dim; e += 32) o_ptr[e] = from_f32<T>(0.f);
+    for (int e = lane; e < v_dim; e += 32) o_ptr[e] = from_f32<T>(0.f);
     return;
   }
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -61,10 +65,14 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
   for (int i = 0; i < OREGS; ++i) acc[i] = 0.f;
   const int* bt = block_table + (long long)req_slots[r] * max_pages;
   const long long kv_row = (long long)num_kv * head_dim;
-
-  for (int base = lo; base <= pos; base += 32) {
+  const long long v_row = (long long)num_kv * v_dim;
+  // two stretches of keys: the kept first positions that lie below the window, then the window
+  const int kept = min(keep_first, lo);
+  for (int part = kept > 0 ? 0 : 1; part < 2; ++part) {
+  const int first = part == 0 ? 0 : lo, last = part == 0 ? kept - 1 : pos;
+  for (int base = first; base <= last; base += 32) {
     const int key = base + lane;
-    const bool valid = key <= pos;
+    const bool valid = key <= last;
     long long slot = -1;
     float s = -INFINITY;
     if (valid) {
@@ -85,25 +93,26 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
     l = l * alpha + warp_sum(p);
 #pragma unroll
     for (int i = 0; i < OREGS; ++i) acc[i] *= alpha;
-    const int n = min(32, pos - base + 1);
+    const int n = min(32, last - base + 1);
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const long long sj = __shfl_sync(0xffffffffu, slot, j);
       if (sj < 0) continue;
-      const T* vp = v_cache + sj * kv_row + (long long)kh * head_dim;
+      const T* vp = v_cache + sj * v_row + (long long)kh * v_dim;
 #pragma unroll
       for (int i = 0; i < OREGS; ++i) {
         const int e = lane + 32 * i;
-        if (e < head_dim) acc[i] += pj * to_f32(vp[e]);
+        if (e < v_dim) acc[i] += pj * to_f32(vp[e]);
       }
     }
     m = m_new;
+  }
   }
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < OREGS; ++i) {
     const int e = lane + 32 * i;
-    if (e < head_dim) o_ptr[e] = from_f32<T>(acc[i] * inv);
+    if (e < v_dim) o_ptr[e] = from_f32<T>(acc[i] * inv);
   }
 }
 
@@ -111,22 +120,54 @@ template <typename T>
 static int launch_generic(const void* q, long long q_row_stride, void* out, const void* k_cache, const void* v_cache,
                           const int* block_table, int max_pages, const int* req_slots, const int* cu_q,
                           const int* kv_len, const int* token_req, int tokens, int num_q, int num_kv, int head_dim, int page_size,
-                          int window, float scale, long long num_pages, int* status, cudaStream_t st) {
+                          int window, float scale, long long num_pages, int* status, cudaStream_t st, int v_dim,
+                          int keep_first) {
   const long long units = (long long)tokens * num_q;
   const long long blocks = (units + ATT_WARPS - 1) / ATT_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
 #define LAUNCH(OREGS)                                                                                             \
   rc = ullm_launch_kernel(paged_attention_generic_kernel<T, OREGS>, dim3((int)blocks), dim3(ATT_WARPS * 32), 0, st, \
       (const T*)q, q_row_stride, (T*)out, (const T*)k_cache, (const T*)v_cache, block_table, max_pages, req_slots,  \
-      cu_q, kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status)
+      cu_q, kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status,       \
+      v_dim, keep_first)
   int rc = ULLM_OK;
-  if (head_dim <= 32) LAUNCH(1);
-  else if (head_dim <= 64) LAUNCH(2);
-  else if (head_dim <= 128) LAUNCH(4);
-  else if (head_dim <= 256) LAUNCH(8);
+  if (v_dim <= 32) LAUNCH(1);
+  else if (v_dim <= 64) LAUNCH(2);
+  else if (v_dim <= 128) LAUNCH(4);
+  else if (v_dim <= 256) LAUNCH(8);
   else LAUNCH(16);
 #undef LAUNCH
   return rc;
+}
+
+// `v_dim`: head size of the values (and of the output); `keep_first`: positions below it stay visible.
+extern "C" int ullm_paged_attention_generic_ex(int dtype, const void* q, long long q_row_stride, void* out,
+                                               const void* k_cache, const void* v_cache, const int* block_table,
+                                               int max_pages, const int* req_slots, const int* cu_q,
+                                               const int* kv_len, const int* token_req, int tokens, int num_q,
+                                               int num_kv, int head_dim, int page_size, int window, float scale,
+                                               long long num_pages, int* status, void* stream, int v_dim,
+                                               int keep_first) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
+    return ULLM_ERR_BAD_SIZE;
+  if (num_q % num_kv != 0 || head_dim > ATT_MAX_HEAD_DIM || window < 0 || v_dim <= 0 || v_dim > ATT_MAX_HEAD_DIM ||
+      keep_first < 0)
+    return ULLM_ERR_UNSUPPORTED;
+  if (tokens == 0) return ULLM_OK;
+  if (dtype == ULLM_DTYPE_F32)
+    return launch_generic<float>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                 kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
+                                 status, st, v_dim, keep_first);
+  if (dtype == ULLM_DTYPE_BF16)
+    return launch_generic<__nv_bfloat16>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                         kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale,
+                                         num_pages, status, st, v_dim, keep_first);
+  if (dtype == ULLM_DTYPE_F16)
+    return launch_generic<__half>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                  kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
+                                  status, st, v_dim, keep_first);
+  return ULLM_ERR_BAD_DTYPE;
 }
 
 extern "C" int ullm_paged_attention_generic(int dtype, const void* q, long long q_row_stride, void* out,
@@ -135,22 +176,7 @@ extern "C" int ullm_paged_attention_generic(int dtype, const void* q, long long 
                                             const int* token_req,
                                             int tokens, int num_q, int num_kv, int head_dim, int page_size, int window,
                                             float scale, long long num_pages, int* status, void* stream) {
-  cudaStream_t st = (cudaStream_t)stream;
-  if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
-    return ULLM_ERR_BAD_SIZE;
-  if (num_q % num_kv != 0 || head_dim > ATT_MAX_HEAD_DIM || window < 0) return ULLM_ERR_UNSUPPORTED;
-  if (tokens == 0) return ULLM_OK;
-  if (dtype == ULLM_DTYPE_F32)
-    return launch_generic<float>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
-                                 kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
-                                 status, st);
-  if (dtype == ULLM_DTYPE_BF16)
-    return launch_generic<__nv_bfloat16>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
-                                         kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale,
-                                         num_pages, status, st);
-  if (dtype == ULLM_DTYPE_F16)
-    return launch_generic<__half>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
-                                  kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
-                                  status, st);
-  return ULLM_ERR_BAD_DTYPE;
+  return ullm_paged_attention_generic_ex(dtype, q, q_row_stride, out, k_cache, v_cache, block_table, max_pages,
+                                         req_slots, cu_q, kv_len, token_req, tokens, num_q, num_kv, head_dim,
+                                         page_size, window, scale, num_pages, status, stream, head_dim, 0);
 }

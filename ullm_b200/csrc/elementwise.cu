@@ -389,3 +389,43 @@ extern "C" int ullm_cast_bf16_f32(const void* in, float* out, long long n, void*
   return ullm_launch_kernel(cast_bf16_f32_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream,
                             (const __nv_bfloat16*)in, out, n);
 }
+
+// ---------------------------------------------------------------------------
+// clamped gated activation: g' = min(g, limit), u' = clamp(u, -limit, limit),
+// out = g' * sigmoid(alpha * g') * (u' + 1), in 32-bit
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void act_mul_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int inter,
+                                       float limit, float alpha) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long n = rows * inter;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / inter;
+    const int c = (int)(i - t * inter);
+    const float g = fminf(to_f32(gu[t * 2 * inter + c]), limit);
+    const float u = fminf(fmaxf(to_f32(gu[t * 2 * inter + inter + c]), -limit), limit);
+    out[i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+extern "C" int ullm_act_mul_clamped(int dtype, const void* gate_up, void* out, int rows, int inter, float limit,
+                                    float alpha, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (rows < 0 || inter <= 0) return ULLM_ERR_BAD_SIZE;
+  if (rows == 0) return ULLM_OK;
+  const long long n = (long long)rows * inter;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const dim3 grid((int)blocks), block(256);
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(act_mul_clamped_kernel<float>, grid, block, 0, st, (const float*)gate_up, (float*)out,
+                              (long long)rows, inter, limit, alpha);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(act_mul_clamped_kernel<__nv_bfloat16>, grid, block, 0, st,
+                              (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, (long long)rows, inter, limit, alpha);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(act_mul_clamped_kernel<__half>, grid, block, 0, st, (const __half*)gate_up,
+                              (__half*)out, (long long)rows, inter, limit, alpha);
+  return ULLM_ERR_BAD_DTYPE;
+}

@@ -1,0 +1,245 @@
+// Matrix memory with exponential gates (the mLSTM recurrence), for any mix of
+// requests in one flat batch: prompt portions of any length beside single
+// decoded tokens.  Per request and head the state is a matrix S [d, dv], a
+// vector n [d] and a running maximum m, all 32-bit, kept in the request's state
+// row between steps:
+//
+//   i_t = cap tanh((a_t + b_i) / cap)                     log input gate (a, c: the gate projections)
+//   f_t = logsigmoid(cap tanh((c_t + b_f) / cap))         log forget gate
+//   m_t = max(f_t + m_{t-1}, i_t)
+//   S_t = exp(f_t + m_{t-1} - m_t) S_{t-1} + exp(i_t - m_t) k_t v_t^T      (n_t alike with k_t alone)
+//   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6),   q_t = q_scale * (projected query)
+//
+// The recurrence is run token by token, so a request's result does not depend on how its tokens were cut into
+// steps.  The parallelism is over requests, heads and the columns of S: a block owns (request, head, a tile of
+// columns); a column's d rows are spread over RS neighbouring lanes (row r belongs to lane r mod RS), which meet
+// in shuffles for the two dot products.  q, k and the tile's v of a chunk of tokens are staged in shared memory,
+// the gates of the chunk are evaluated once per block.
+//
+// State row layout (floats): S^T as [heads][dv][d], then n [heads][d], then m [heads].
+//
+// A second kernel finishes the mixer's head: per (token, head) o / sqrt(mean(o^2) + eps) * w * sigmoid(g).
+#include "common.cuh"
+
+#define MLSTM_THREADS 128
+#define MLSTM_RPT 16       // rows of S a thread holds at most
+#define MLSTM_MAX_DIM 512  // = 32 lanes * MLSTM_RPT
+
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+template <typename T>
+__global__ void __launch_bounds__(MLSTM_THREADS)
+mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off, int k_off, int v_off,
+                        const float* __restrict__ gates, const float* __restrict__ bias_i,
+                        const float* __restrict__ bias_f, float* __restrict__ state, long long state_stride,
+                        const int* __restrict__ cu_q, const int* __restrict__ req_slots,
+                        const int* __restrict__ token_req, float* __restrict__ out, int heads, int dim, int vdim,
+                        int rs, int chunk, float q_scale, float cap, int num_slots, int* status) {
+  extern __shared__ float sm[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int req = blockIdx.z, head = blockIdx.y;
+  const int cols_per_block = MLSTM_THREADS / rs;
+  const int lane_row = threadIdx.x % rs;          // which rows: lane_row, lane_row + rs, ...
+  const int col_in_block = threadIdx.x / rs;
+  const int col = blockIdx.x * cols_per_block + col_in_block;
+  const bool col_ok = col < vdim;
+  const int t0 = cu_q[req], t1 = cu_q[req + 1];
+  if (t1 <= t0) return;
+  const bool padding = token_req[t0] < 0;  // a row that belongs to no request: zeros out, no state touched
+  const int slot = req_slots[req];
+  if (!padding && (slot < 0 || slot >= num_slots)) {
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, req, slot);
+    return;
+  }
+  if (padding) {
+    if (lane_row == 0 && col_ok)
+      for (int t = t0; t < t1; ++t) out[((long long)t * heads + head) * vdim + col] = 0.f;
+    return;
+  }
+  float* sq = sm;                        // [chunk][dim]
+  float* sk = sq + chunk * dim;          // [chunk][dim]
+  float* sv = sk + chunk * dim;          // [chunk][cols_per_block]
+  float* sgi = sv + chunk * cols_per_block;  // [chunk]
+  float* sgf = sgi + chunk;              // [chunk]
+
+  float* st_row = state + (long long)slot * state_stride;
+  float* st_S = st_row + ((long long)head * vdim + (col_ok ? col : 0)) * dim;
+  float* st_n = st_row + (long long)heads * vdim * dim + (long long)head * dim;
+  float* st_m = st_row + (long long)heads * vdim * dim + (long long)heads * dim + head;
+
+  float S[MLSTM_RPT], n[MLSTM_RPT];
+#pragma unroll
+  for (int i = 0; i < MLSTM_RPT; ++i) {
+    const int r = lane_row + rs * i;
+    const bool on = r < dim;
+    S[i] = (on && col_ok) ? st_S[r] : 0.f;
+    n[i] = on ? st_n[r] : 0.f;
+  }
+  float m = *st_m;
+  const float bi = bias_i != nullptr ? bias_i[head] : 0.f, bf = bias_f != nullptr ? bias_f[head] : 0.f;
+
+  for (int c0 = t0; c0 < t1; c0 += chunk) {
+    const int cn = min(chunk, t1 - c0);
+    __syncthreads();  // the chunk before has been used up
+    for (int e = threadIdx.x; e < cn * dim; e += MLSTM_THREADS) {
+      const int t = e / dim, r = e - t * dim;
+      const T* row = qkv + (long long)(c0 + t) * row_stride;
+      sq[e] = to_f32(row[q_off + head * dim + r]) * q_scale;
+      sk[e] = to_f32(row[k_off + head * dim + r]);
+    }
+    for (int e = threadIdx.x; e < cn * cols_per_block; e += MLSTM_THREADS) {
+      const int t = e / cols_per_block, j = e - t * cols_per_block;
+      const int cj = blockIdx.x * cols_per_block + j;
+      sv[e] = cj < vdim ? to_f32(qkv[(long long)(c0 + t) * row_stride + v_off + head * vdim + cj]) : 0.f;
+    }
+    if (threadIdx.x < cn) {
+      const float* g = gates + (long long)(c0 + threadIdx.x) * 2 * heads;
+      sgi[threadIdx.x] = cap * tanhf((g[head] + bi) / cap);
+      sgf[threadIdx.x] = log_sigmoid(cap * tanhf((g[heads + head] + bf) / cap));
+    }
+    __syncthreads();
+    for (int t = 0; t < cn; ++t) {
+      const float fi = sgf[t], ii = sgi[t];
+      const float m_new = fmaxf(fi + m, ii);
+      const float keep = expf(fi + m - m_new), take = expf(ii - m_new);
+      m = m_new;
+      const float tv = take * sv[t * cols_per_block + col_in_block];
+      const float* kq = sk + t * dim;
+      const float* qq = sq + t * dim;
+      float dot = 0.f, ndot = 0.f;
+#pragma unroll
+      for (int i = 0; i < MLSTM_RPT; ++i) {
+        const int r = lane_row + rs * i;
+        if (r < dim) {
+          const float kr = kq[r], qr = qq[r];
+          S[i] = fmaf(keep, S[i], kr * tv);
+          n[i] = fmaf(keep, n[i], take * kr);
+          dot = fmaf(S[i], qr, dot);
+          ndot = fmaf(n[i], qr, ndot);
+        }
+      }
+      for (int o = rs >> 1; o > 0; o >>= 1) {
+        dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
+      }
+      if (lane_row == 0 && col_ok) {
+        const float den = fmaxf(fabsf(ndot), expf(-m)) + 1e-6f;
+        out[((long long)(c0 + t) * heads + head) * vdim + col] = dot / den;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < MLSTM_RPT; ++i) {
+    const int r = lane_row + rs * i;
+    if (r < dim) {
+      if (col_ok) st_S[r] = S[i];
+      if (blockIdx.x == 0 && col_in_block == 0) st_n[r] = n[i];
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) *st_m = m;
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w[h, :] * sigmoid(g[t, h, :]); one warp per (token, head).
+template <typename T>
+__global__ void mlstm_out_gate_kernel(const float* __restrict__ o, const T* __restrict__ g, long long g_stride,
+                                      const float* __restrict__ w, T* __restrict__ out, long long units, int heads,
+                                      int vdim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (unit >= units) return;
+  const long long t = unit / heads;
+  const int h = (int)(unit - t * heads);
+  const float* src = o + unit * vdim;
+  float ss = 0.f;
+  for (int e = lane; e < vdim; e += 32) ss += src[e] * src[e];
+  ss = warp_sum(ss);
+  const float rstd = 1.f / sqrtf(ss / (float)vdim + eps);
+  const T* gr = g + t * g_stride + (long long)h * vdim;
+  for (int e = lane; e < vdim; e += 32) {
+    const float gate = 1.f / (1.f + expf(-to_f32(gr[e])));
+    out[unit * vdim + e] = from_f32<T>(src[e] * rstd * w[h * vdim + e] * gate);
+  }
+}
+
+static int mlstm_rs(int dim) {
+  int rs = 1;
+  while (rs * MLSTM_RPT < dim) rs <<= 1;
+  return rs;
+}
+
+extern "C" int ullm_mlstm_supported(int heads, int dim, int vdim) {
+  return heads > 0 && dim > 0 && vdim > 0 && dim <= MLSTM_MAX_DIM;
+}
+
+// Floats of one request's state row.
+extern "C" long long ullm_mlstm_state_floats(int heads, int dim, int vdim) {
+  return (long long)heads * vdim * dim + (long long)heads * dim + heads;
+}
+
+template <typename T>
+static int mlstm_launch(const void* qkv, long long row_stride, int q_off, int k_off, int v_off, const float* gates,
+                        const float* bias_i, const float* bias_f, float* state, long long state_stride,
+                        const int* cu_q, const int* req_slots, const int* token_req, float* out, int requests,
+                        int heads, int dim, int vdim, float q_scale, float cap, int num_slots, int* status,
+                        cudaStream_t st) {
+  const int rs = mlstm_rs(dim);
+  const int cols = MLSTM_THREADS / rs;
+  const int chunk = dim <= 256 ? 16 : 8;
+  const size_t smem = (size_t)(2 * chunk * dim + chunk * cols + 2 * chunk) * sizeof(float);
+  const dim3 grid((vdim + cols - 1) / cols, heads, requests);
+  return ullm_launch_kernel(mlstm_recurrence_kernel<T>, grid, dim3(MLSTM_THREADS), smem, st, (const T*)qkv,
+                            row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state, state_stride, cu_q,
+                            req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale, cap, num_slots, status);
+}
+
+// qkv: rows of `row_stride` elements that hold q [heads, dim] at q_off, k [heads, dim] at k_off and v [heads, vdim]
+// at v_off.  gates: [tokens, 2 heads] float32, the input-gate projections then the forget-gate projections (biases
+// not yet added).  state: [num_slots, state_stride] float32.  out: [tokens, heads, vdim] float32.
+extern "C" int ullm_mlstm_recurrence(int dtype, const void* qkv, long long row_stride, int q_off, int k_off,
+                                     int v_off, const float* gates, const float* bias_i, const float* bias_f,
+                                     float* state, long long state_stride, const int* cu_q, const int* req_slots,
+                                     const int* token_req, float* out, int requests, int heads, int dim, int vdim,
+                                     float q_scale, float cap, int num_slots, int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (requests < 0 || !ullm_mlstm_supported(heads, dim, vdim)) return ULLM_ERR_UNSUPPORTED;
+  if (state_stride < ullm_mlstm_state_floats(heads, dim, vdim) || cap <= 0.f) return ULLM_ERR_BAD_SIZE;
+  if (requests == 0) return ULLM_OK;
+  if (requests > 65535 || heads > 65535) return ULLM_ERR_BAD_SIZE;
+  if (dtype == ULLM_DTYPE_F32)
+    return mlstm_launch<float>(qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state, state_stride,
+                               cu_q, req_slots, token_req, out, requests, heads, dim, vdim, q_scale, cap, num_slots,
+                               status, st);
+  if (dtype == ULLM_DTYPE_BF16)
+    return mlstm_launch<__nv_bfloat16>(qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state,
+                                       state_stride, cu_q, req_slots, token_req, out, requests, heads, dim, vdim,
+                                       q_scale, cap, num_slots, status, st);
+  if (dtype == ULLM_DTYPE_F16)
+    return mlstm_launch<__half>(qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state, state_stride,
+                                cu_q, req_slots, token_req, out, requests, heads, dim, vdim, q_scale, cap, num_slots,
+                                status, st);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_mlstm_out_gate(int dtype, const float* o, const void* g, long long g_stride, const float* w,
+                                   void* out, int tokens, int heads, int vdim, float eps, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || heads <= 0 || vdim <= 0) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  const long long units = (long long)tokens * heads;
+  const long long blocks = (units + 3) / 4;
+  if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
+  const dim3 grid((int)blocks), block(128);
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(mlstm_out_gate_kernel<float>, grid, block, 0, st, o, (const float*)g, g_stride, w,
+                              (float*)out, units, heads, vdim, eps);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(mlstm_out_gate_kernel<__nv_bfloat16>, grid, block, 0, st, o, (const __nv_bfloat16*)g,
+                              g_stride, w, (__nv_bfloat16*)out, units, heads, vdim, eps);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(mlstm_out_gate_kernel<__half>, grid, block, 0, st, o, (const __half*)g, g_stride, w,
+                              (__half*)out, units, heads, vdim, eps);
+  return ULLM_ERR_BAD_DTYPE;
+}

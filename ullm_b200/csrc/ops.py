@@ -227,6 +227,19 @@ class Kernels:
             "ullm_linear_tcgen05_large": [P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_decode_attention_tcgen05": [P, LL, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, F, LL, P, P],
             "ullm_lt_linear": [P, P, P, I, I, I, I, P, LL, I, P, LL, P],
+            "ullm_paged_attention_generic_ex": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I],
+            "ullm_qk_norm_rope_store_ex": [I, P, I, I, I, I, P, P, F, P, P, I, I, P, P, P, P, LL, P, P, I, I],
+            "ullm_act_mul_clamped": [I, P, P, I, I, F, F, P],
+            "ullm_embed_scaled": [I, P, P, P, P, I, I, I, F, P, P, P, P, P, P, P],
+            "ullm_norm_scale_add": [I, P, P, P, P, I, I, F, F, P],
+            "ullm_rmsnorm_rows_f32": [I, P, P, P, P, I, I, I, F, P, P],
+            "ullm_cast_rows_f32": [I, P, P, LL, P],
+            "ullm_mlstm_recurrence": [I, P, LL, I, I, I, P, P, P, P, LL, P, P, P, P, I, I, I, I, F, F, I, P, P],
+            "ullm_mlstm_out_gate": [I, P, P, LL, P, P, I, I, I, F, P],
+            "ullm_moe_route": [P, P, P, I, I, I, I, I, P],
+            "ullm_moe_arrange": [P, I, I, P, P, P, P],
+            "ullm_moe_grouped_linear": [I, P, LL, P, LL, P, P, P, P, I, I, I, I, I, I, I, I, P],
+            "ullm_moe_combine": [I, P, P, P, P, I, I, I, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -234,6 +247,10 @@ class Kernels:
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = c_int
+        L.ullm_mlstm_supported.argtypes = [I, I, I]
+        L.ullm_mlstm_supported.restype = c_int
+        L.ullm_mlstm_state_floats.argtypes = [I, I, I]
+        L.ullm_mlstm_state_floats.restype = c_longlong
         L.ullm_wait_selftest.argtypes = [I, P, P, P]
         L.ullm_wait_selftest.restype = c_int
         L.ullm_decode_attention_supported.argtypes = [I, I, I]
@@ -682,16 +699,201 @@ class Kernels:
         self._check(self.lib.ullm_act_mul(_DT[gate_up.dtype], act, _ptr(gate_up), _ptr(out), rows, inter, _stream()),
                     "act_mul")
 
+    # -- a residual stream kept in 32-bit ---------------------------------------
+    @_timed("embedding")
+    def embed_scaled(self, ids, table, stream, copy=None, scale: float = 1.0, inv_freq=None, positions=None,
+                     last_tokens=None, token_req=None, req_slots=None):
+        """stream[t] (float32) = table[ids[t]] * scale, plus the sinusoid of positions[t] when `inv_freq`
+        (float32 [ceil(hidden / 2)]) is given; `copy` (the table's dtype, optional) gets the rounded stream.
+        An id of -1 is the request's last sampled token, as in `embedding`."""
+        _need(ids, "ids", torch.int32)
+        _need(table, "table")
+        _need(stream, "stream", torch.float32)
+        T, H = stream.shape
+        if ids.numel() < T or table.shape[1] != H:
+            raise KernelError(f"embed_scaled: ids {tuple(ids.shape)}, table {tuple(table.shape)}, stream {tuple(stream.shape)}")
+        if copy is not None:
+            _need(copy, "copy", table.dtype)
+            if copy.shape != stream.shape:
+                raise KernelError("embed_scaled: the copy's shape differs from the stream's")
+        if inv_freq is not None:
+            _need(inv_freq, "inv_freq", torch.float32)
+            _need(positions, "positions", torch.int32)
+            if inv_freq.numel() < (H + 1) // 2 or positions.numel() < T:
+                raise KernelError("embed_scaled: the frequency table or the positions are too short")
+        if last_tokens is not None:
+            for t_, n_ in ((last_tokens, "last_tokens"), (token_req, "token_req"), (req_slots, "req_slots")):
+                _need(t_, n_, torch.int32)
+        self._check(self.lib.ullm_embed_scaled(_DT[table.dtype], _ptr(ids), _ptr(table), _ptr(stream), _ptr(copy), T, H,
+                                               table.shape[0], float(scale), _ptr(inv_freq), _ptr(positions),
+                                               _ptr(last_tokens), _ptr(token_req), _ptr(req_slots), _ptr(self.status),
+                                               _stream()), "embed_scaled")
+
+    @_timed("add_rmsnorm")
+    def norm_scale_add(self, a, stream, weight, eps: float, mult: float, copy=None):
+        """stream (float32, in place) += mult * weight * a / sqrt(mean(a^2) + eps); `copy` (a's dtype, optional)
+        gets the rounded stream."""
+        _need(a, "a")
+        _need(stream, "stream", torch.float32)
+        _need(weight, "weight", torch.float32)
+        rows, cols = a.shape
+        if stream.shape != a.shape or weight.numel() != cols:
+            raise KernelError(f"norm_scale_add: a {tuple(a.shape)}, stream {tuple(stream.shape)}, weight {tuple(weight.shape)}")
+        if copy is not None:
+            _need(copy, "copy", a.dtype)
+            if copy.shape != a.shape:
+                raise KernelError("norm_scale_add: the copy's shape differs")
+        self._check(self.lib.ullm_norm_scale_add(_DT[a.dtype], _ptr(a), _ptr(stream), _ptr(weight), _ptr(copy), rows, cols,
+                                                 float(eps), float(mult), _stream()), "norm_scale_add")
+
+    @_timed("add_rmsnorm")
+    def rmsnorm_rows_f32(self, stream, rows, weight, eps: float, out):
+        """out[r] = weight * s / sqrt(mean(s^2) + eps) for s = stream[rows[r]] (float32 stream, `rows` int32 or
+        None for all rows in order), rounded to out's dtype."""
+        _need(stream, "stream", torch.float32)
+        _need(weight, "weight", torch.float32)
+        _need(out, "out")
+        R, C = out.shape
+        if stream.shape[1] != C or weight.numel() != C or (rows is None and stream.shape[0] < R):
+            raise KernelError(f"rmsnorm_rows_f32: stream {tuple(stream.shape)}, out {tuple(out.shape)}")
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+            if rows.numel() < R:
+                raise KernelError("rmsnorm_rows_f32: fewer row indices than output rows")
+        self._check(self.lib.ullm_rmsnorm_rows_f32(_DT[out.dtype], _ptr(stream), _ptr(rows), _ptr(weight), _ptr(out), R, C,
+                                                   stream.shape[0], float(eps), _ptr(self.status), _stream()),
+                    "rmsnorm_rows_f32")
+
+    @_timed("add_rmsnorm")
+    def cast_rows_f32(self, src, out):
+        _need(src, "src", torch.float32)
+        _need(out, "out")
+        if src.shape != out.shape:
+            raise KernelError("cast_rows_f32: shapes differ")
+        self._check(self.lib.ullm_cast_rows_f32(_DT[out.dtype], _ptr(src), _ptr(out), src.numel(), _stream()), "cast_rows_f32")
+
+    @_timed("act_mul")
+    def act_mul_clamped(self, gate_up, out, limit: float, alpha: float):
+        """out = g' * sigmoid(alpha g') * (u' + 1) with g' = min(gate, limit), u' = clamp(up, -limit, limit)."""
+        _need(gate_up, "gate_up")
+        _need(out, "out", gate_up.dtype)
+        rows, inter = out.shape
+        if gate_up.shape != (rows, 2 * inter):
+            raise KernelError(f"act_mul_clamped: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_act_mul_clamped(_DT[gate_up.dtype], _ptr(gate_up), _ptr(out), rows, inter, float(limit),
+                                                  float(alpha), _stream()), "act_mul_clamped")
+
+    # -- matrix memory (mLSTM) ----------------------------------------------------
+    def mlstm_supported(self, heads: int, dim: int, vdim: int) -> bool:
+        return bool(self.lib.ullm_mlstm_supported(heads, dim, vdim))
+
+    def mlstm_state_floats(self, heads: int, dim: int, vdim: int) -> int:
+        return int(self.lib.ullm_mlstm_state_floats(heads, dim, vdim))
+
+    @_timed("mlstm")
+    def mlstm_recurrence(self, qkv, q_off, k_off, v_off, gates, bias_i, bias_f, state, cu_q, req_slots, token_req, out,
+                         requests, heads, dim, vdim, q_scale, cap):
+        """The recurrence of csrc/mlstm.cu over the step's tokens, from and into the requests' state rows.
+        qkv [T, *]: q, k, v at the given column offsets; gates [T, 2 heads] float32; out [T, heads * vdim] float32."""
+        _need(qkv, "qkv")
+        _need(gates, "gates", torch.float32)
+        _need(state, "state", torch.float32)
+        _need(out, "out", torch.float32)
+        for t_, n_ in ((bias_i, "input gate bias"), (bias_f, "forget gate bias")):
+            if t_ is not None:
+                _need(t_, n_, torch.float32)
+        for t_, n_ in ((cu_q, "cu_q"), (req_slots, "req_slots"), (token_req, "token_req")):
+            _need(t_, n_, torch.int32)
+        T = qkv.shape[0]
+        if gates.shape != (T, 2 * heads) or out.shape != (T, heads * vdim) or state.dim() != 2:
+            raise KernelError(f"mlstm_recurrence: qkv {tuple(qkv.shape)}, gates {tuple(gates.shape)}, out {tuple(out.shape)}")
+        if max(q_off, k_off) + heads * dim > qkv.shape[1] or v_off + heads * vdim > qkv.shape[1]:
+            raise KernelError("mlstm_recurrence: q, k or v lie outside the rows")
+        self._check(self.lib.ullm_mlstm_recurrence(
+            _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), q_off, k_off, v_off, _ptr(gates), _ptr(bias_i), _ptr(bias_f),
+            _ptr(state), state.stride(0), _ptr(cu_q), _ptr(req_slots), _ptr(token_req), _ptr(out), requests, heads, dim,
+            vdim, float(q_scale), float(cap), state.shape[0], _ptr(self.status), _stream()),
+            f"mlstm_recurrence (heads {heads}, dim {dim}, vdim {vdim})")
+
+    @_timed("mlstm")
+    def mlstm_out_gate(self, o, g, weight, eps, out, heads, vdim):
+        """out = o / sqrt(mean over a head of o^2 + eps) * weight * sigmoid(g); o float32 [T, heads * vdim], g a
+        view [T, heads * vdim] of the projection's rows (any row stride)."""
+        _need(o, "o", torch.float32)
+        _need(g, "g", out.dtype, contiguous=False)
+        _need(weight, "weight", torch.float32)
+        _need(out, "out")
+        T = o.shape[0]
+        if o.shape != (T, heads * vdim) or g.shape != o.shape or out.shape != o.shape or g.stride(1) != 1 or weight.numel() != heads * vdim:
+            raise KernelError(f"mlstm_out_gate: o {tuple(o.shape)}, g {tuple(g.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_mlstm_out_gate(_DT[out.dtype], _ptr(o), _ptr(g), g.stride(0), _ptr(weight), _ptr(out), T,
+                                                 heads, vdim, float(eps), _stream()), "mlstm_out_gate")
+
+    # -- routed experts -----------------------------------------------------------
+    @_timed("moe")
+    def moe_route(self, logits, choice, weight, top: int, softmax_scores: bool = False, renormalize: bool = False):
+        _need(logits, "router logits", torch.float32)
+        _need(choice, "choice", torch.int32)
+        _need(weight, "weight", torch.float32)
+        T, E = logits.shape
+        if choice.numel() < T * top or weight.numel() < T * top:
+            raise KernelError("moe_route: outputs too small")
+        self._check(self.lib.ullm_moe_route(_ptr(logits), _ptr(choice), _ptr(weight), T, E, top, int(softmax_scores),
+                                            int(renormalize), _stream()), f"moe_route ({E} experts, top {top})")
+
+    @_timed("moe")
+    def moe_arrange(self, choice, pairs: int, experts: int, offsets, sorted_pairs, place):
+        for t_, n_ in ((choice, "choice"), (offsets, "offsets"), (sorted_pairs, "sorted"), (place, "place")):
+            _need(t_, n_, torch.int32)
+        if offsets.numel() < experts + 1 or sorted_pairs.numel() < pairs or place.numel() < pairs:
+            raise KernelError("moe_arrange: outputs too small")
+        self._check(self.lib.ullm_moe_arrange(_ptr(choice), pairs, experts, _ptr(offsets), _ptr(sorted_pairs), _ptr(place),
+                                              _stream()), f"moe_arrange ({experts} experts)")
+
+    @_timed("moe", lambda x, weights, *r: weights.numel() * weights.element_size())
+    def moe_grouped_linear(self, x, weights, offsets, sorted_pairs, pair_weight, out, top: int, rows_from_pairs: bool,
+                           gated: bool, act: int = 0):
+        """out[p] = W_e . x[row(p)] for every place p of every expert e (see csrc/moe.cu); weights
+        [experts, (2 if gated) * n_out, k]."""
+        _need(x, "x")
+        _need(weights, "expert weights", x.dtype)
+        _need(out, "out", x.dtype)
+        E, N, K = weights.shape
+        pairs, n_out = out.shape
+        if N != (2 if gated else 1) * n_out or x.shape[1] != K:
+            raise KernelError(f"moe_grouped_linear: x {tuple(x.shape)}, weights {tuple(weights.shape)}, out {tuple(out.shape)}")
+        if pair_weight is not None:
+            _need(pair_weight, "pair weights", torch.float32)
+        self._check(self.lib.ullm_moe_grouped_linear(
+            _DT[x.dtype], _ptr(x), x.stride(0), _ptr(weights), weights.stride(0), _ptr(offsets), _ptr(sorted_pairs),
+            _ptr(pair_weight), _ptr(out), pairs, E, top, int(rows_from_pairs), n_out, K, int(gated), act, _stream()),
+            f"moe_grouped_linear ({E} experts, {N} x {K})")
+
+    @_timed("moe")
+    def moe_combine(self, rows, place, pair_weight, y, top: int):
+        _need(rows, "rows")
+        _need(place, "place", torch.int32)
+        _need(y, "y", rows.dtype)
+        T, C = y.shape
+        if rows.shape[1] != C or rows.shape[0] < T * top:
+            raise KernelError("moe_combine: shapes differ")
+        self._check(self.lib.ullm_moe_combine(_DT[y.dtype], _ptr(rows), _ptr(place), _ptr(pair_weight), _ptr(y), T, top, C,
+                                              _stream()), "moe_combine")
+
     def check_attention_sizes(self, *a):
         check_attention_sizes(*a)
 
     @_timed("qk_norm_rope_store")
     def qk_norm_rope_store(self, qkv, num_q, num_kv, head_dim, q_w, k_w, eps, cos, sin, rotary_dim, positions,
-                           slot_mapping, k_pages, v_pages):
+                           slot_mapping, k_pages, v_pages, v_dim: int | None = None, kv_in_row: bool = True):
+        """`v_dim`: head size of the values when it differs from the keys'; `kv_in_row` False: the rows hold the
+        query heads only (nothing is stored)."""
         _need(qkv, "qkv")
         T, W = qkv.shape
-        if W != (num_q + 2 * num_kv) * head_dim:
-            raise KernelError(f"qk_norm_rope_store: qkv row length {W} != (Hq + 2 Hkv) * D")
+        v_dim = head_dim if v_dim is None else v_dim
+        want = num_q * head_dim + ((num_kv * (head_dim + v_dim)) if kv_in_row else 0)
+        if W != want:
+            raise KernelError(f"qk_norm_rope_store: qkv row length {W} != {want} (Hq D + Hkv (D + Dv))")
         for t, n in ((q_w, "q_norm weight"), (k_w, "k_norm weight"), (cos, "cos table"), (sin, "sin table")):
             if t is not None:
                 _need(t, n, torch.float32)
@@ -702,17 +904,28 @@ class Kernels:
             max_pos = cos.shape[0]
             _need(positions, "positions", torch.int32)
         num_slots = 0
+        if not kv_in_row:
+            slot_mapping = None
         if slot_mapping is not None:
             _need(slot_mapping, "slot_mapping", torch.int32)
             _need(k_pages, "k_pages", qkv.dtype)
             _need(v_pages, "v_pages", qkv.dtype)
-            if k_pages.shape[-2:] != (num_kv, head_dim) or v_pages.shape != k_pages.shape:
-                raise KernelError(f"qk_norm_rope_store: pages {tuple(k_pages.shape)} do not end in (Hkv, D)")
+            if k_pages.shape[-2:] != (num_kv, head_dim) or v_pages.shape[-2:] != (num_kv, v_dim) \
+                    or v_pages.shape[:-1] != k_pages.shape[:-1]:
+                raise KernelError(f"qk_norm_rope_store: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not end "
+                                  f"in (Hkv, D) / (Hkv, Dv)")
             num_slots = k_pages.numel() // (num_kv * head_dim)
-        self._check(self.lib.ullm_qk_norm_rope_store(
-            _DT[qkv.dtype], _ptr(qkv), T, num_q, num_kv, head_dim, _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos),
-            _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages),
-            num_slots, _ptr(self.status), _stream()), f"qk_norm_rope_store (head_dim {head_dim})")
+        if v_dim == head_dim and kv_in_row:
+            code = self.lib.ullm_qk_norm_rope_store(
+                _DT[qkv.dtype], _ptr(qkv), T, num_q, num_kv, head_dim, _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos),
+                _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages),
+                num_slots, _ptr(self.status), _stream())
+        else:
+            code = self.lib.ullm_qk_norm_rope_store_ex(
+                _DT[qkv.dtype], _ptr(qkv), T, num_q, num_kv, head_dim, _ptr(q_w), _ptr(k_w), float(eps), _ptr(cos),
+                _ptr(sin), rotary_dim, max_pos, _ptr(positions), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages),
+                num_slots, _ptr(self.status), _stream(), v_dim, int(kv_in_row))
+        self._check(code, f"qk_norm_rope_store (head_dim {head_dim})")
 
     @_timed("qk_norm_rope_store")
     def qk_norm_in_place(self, qkv, num_q, num_kv, head_dim, q_w, k_w, eps):
@@ -829,7 +1042,8 @@ class Kernels:
 
     @_timed("attention")
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q, num_kv,
-                        head_dim, page_size, window, scale, ctx=None, fuse=None, ragged: bool = False):
+                        head_dim, page_size, window, scale, ctx=None, fuse=None, ragged: bool = False,
+                        v_dim: int | None = None, keep_first: int = 0):
         """Attention of every row of the flat batch over its request's pages.
         `qkv` holds q in its first num_q * head_dim columns.  `fuse` (only after `decode_fusion_applies` said
         yes): q, k and v are as the projection left them, and the kernel norms, rotates and stores them itself;
@@ -842,11 +1056,25 @@ class Kernels:
         for t, n in ((block_table, "block_table"), (req_slots, "req_slots"), (cu_q, "cu_q"), (kv_len, "kv_len"), (token_req, "token_req")):
             _need(t, n, torch.int32)
         T = out.shape[0]
-        if out.shape[1] != num_q * head_dim or qkv.shape[0] < T:
+        v_dim = head_dim if v_dim is None else v_dim
+        if out.shape[1] != num_q * v_dim or qkv.shape[0] < T:
             raise KernelError(f"paged_attention: out {tuple(out.shape)}, qkv {tuple(qkv.shape)}")
-        if k_pages.shape[-3:] != (page_size, num_kv, head_dim):
-            raise KernelError(f"paged_attention: pages {tuple(k_pages.shape)} != [*, {page_size}, {num_kv}, {head_dim}]")
+        if k_pages.shape[-3:] != (page_size, num_kv, head_dim) or v_pages.shape[-3:] != (page_size, num_kv, v_dim):
+            raise KernelError(f"paged_attention: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} != "
+                              f"[*, {page_size}, {num_kv}, {head_dim} / {v_dim}]")
         num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
+        if v_dim != head_dim or keep_first > 0:
+            # values of a head size of their own, or first positions that stay visible behind the window: the
+            # general kernel (the tensor-core kernels take neither)
+            if fuse is not None:
+                raise KernelError("paged_attention: q and k were left unprepared, but the general kernel takes this step")
+            self.attention_path = "generic"
+            self._check(self.lib.ullm_paged_attention_generic_ex(
+                _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), _ptr(token_req), T, num_q, num_kv,
+                head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream(), v_dim,
+                int(keep_first)), f"paged_attention (head_dim {head_dim}, values {v_dim}, first {keep_first} kept)")
+            return
         decode_ok = (ctx is not None and qkv.dtype == torch.bfloat16
                      and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv))
         if decode_ok and ctx.decode_only and T == ctx.num_requests:

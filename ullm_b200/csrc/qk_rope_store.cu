@@ -21,12 +21,16 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                           int rotary_dim, int max_positions, const int* __restrict__ positions,
                                           const int* __restrict__ slot_mapping, T* k_cache, T* v_cache,
-                                          long long num_slots, int* status, int k_in_place) {
+                                          long long num_slots, int* status, int k_in_place, int v_dim,
+                                          int kv_in_row) {
+  // v_dim: head size of the values; kv_in_row 0: a row holds the query heads only (the keys and values are
+  // another execution's)
   __shared__ float sh[QK_WARPS][QK_MAX_HEAD_DIM];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads = num_q + 2 * num_kv;
+  const int heads = num_q + (kv_in_row ? 2 * num_kv : 0);
+  const long long row_len = (long long)(num_q + (kv_in_row ? num_kv : 0)) * head_dim + (kv_in_row ? (long long)num_kv * v_dim : 0);
   const long long unit = (long long)blockIdx.x * QK_WARPS + warp;
   if (unit >= (long long)tokens * heads) return;
   const int t = (int)(unit / heads);
@@ -46,12 +50,13 @@ __global__ void qk_norm_rope_store_kernel(T* qkv, int tokens, int num_q, int num
       return;
     }
   }
-  T* src = qkv + (long long)t * heads * head_dim + (long long)h * head_dim;
+  T* src = qkv + (long long)t * row_len + (long long)h * head_dim;
   float* y = sh[warp];
   if (!is_q && !is_k) {  // value head: plain copy
     const int kvh = h - num_q - num_kv;
-    T* dst = v_cache + (slot * num_kv + kvh) * head_dim;
-    for (int e = lane; e < head_dim; e += 32) dst[e] = src[e];
+    src = qkv + (long long)t * row_len + (long long)(num_q + num_kv) * head_dim + (long long)kvh * v_dim;
+    T* dst = v_cache + (slot * num_kv + kvh) * v_dim;
+    for (int e = lane; e < v_dim; e += 32) dst[e] = src[e];
     return;
   }
   const float* w = is_q ? q_w : k_w;
@@ -204,17 +209,19 @@ static int qk_norm_rope_store_impl(int dtype, void* qkv, int tokens, int num_q, 
                                    const float* q_w, const float* k_w, float eps, const float* cos_t,
                                    const float* sin_t, int rotary_dim, int max_positions, const int* positions,
                                    const int* slot_mapping, void* k_cache, void* v_cache, long long num_slots,
-                                   int* status, void* stream, int k_in_place) {
+                                   int* status, void* stream, int k_in_place, int v_dim = 0, int kv_in_row = 1) {
   cudaStream_t st = (cudaStream_t)stream;
+  if (v_dim <= 0) v_dim = head_dim;
   if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0) return ULLM_ERR_BAD_SIZE;
+  if (v_dim > QK_MAX_HEAD_DIM) return ULLM_ERR_UNSUPPORTED;
   if (head_dim > QK_MAX_HEAD_DIM || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
     return ULLM_ERR_UNSUPPORTED;
   if (rotary_dim > 0 && (cos_t == nullptr || sin_t == nullptr || positions == nullptr)) return ULLM_ERR_BAD_SIZE;
   if (tokens == 0) return ULLM_OK;
-  const long long units = (long long)tokens * (num_q + 2 * num_kv);
+  const long long units = (long long)tokens * (num_q + (kv_in_row ? 2 * num_kv : 0));
   const long long blocks = (units + QK_WARPS - 1) / QK_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
-  if (!k_in_place && dtype == ULLM_DTYPE_BF16 && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128) &&
+  if (!k_in_place && kv_in_row && v_dim == head_dim && dtype == ULLM_DTYPE_BF16 && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128) &&
       (uintptr_t)qkv % 8 == 0 && (slot_mapping == nullptr || ((uintptr_t)k_cache % 8 == 0 && (uintptr_t)v_cache % 8 == 0))) {
     const int warps = 8;
     const int steps = (long long)tokens * (num_q + 2 * num_kv) >= 8192 ? 6 : 1;
@@ -235,15 +242,15 @@ static int qk_norm_rope_store_impl(int dtype, void* qkv, int tokens, int num_q, 
   if (dtype == ULLM_DTYPE_F32)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<float>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (float*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
-        positions, slot_mapping, (float*)k_cache, (float*)v_cache, num_slots, status, k_in_place);
+        positions, slot_mapping, (float*)k_cache, (float*)v_cache, num_slots, status, k_in_place, v_dim, kv_in_row);
   else if (dtype == ULLM_DTYPE_BF16)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (__nv_bfloat16*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
-        positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots, status, k_in_place);
+        positions, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_slots, status, k_in_place, v_dim, kv_in_row);
   else if (dtype == ULLM_DTYPE_F16)
     return ullm_launch_kernel(qk_norm_rope_store_kernel<__half>, dim3((int)blocks), dim3(QK_WARPS * 32), 0, st,
         (__half*)qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim, max_positions,
-        positions, slot_mapping, (__half*)k_cache, (__half*)v_cache, num_slots, status, k_in_place);
+        positions, slot_mapping, (__half*)k_cache, (__half*)v_cache, num_slots, status, k_in_place, v_dim, kv_in_row);
   else
     return ULLM_ERR_BAD_DTYPE;
   return ullm_launch_status();
@@ -265,4 +272,16 @@ extern "C" int ullm_qk_norm_in_place(int dtype, void* qkv, int tokens, int num_q
                                      const float* q_w, const float* k_w, float eps, int* status, void* stream) {
   return qk_norm_rope_store_impl(dtype, qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, nullptr, nullptr, 0, 0,
                                  nullptr, nullptr, nullptr, nullptr, 0, status, stream, 1);
+}
+
+// The general form: values of head size `v_dim` (rows are q heads | k heads | v heads), and rows that hold the
+// query heads only (`kv_in_row` 0: nothing is stored, the queries are normed and rotated where they lie).
+extern "C" int ullm_qk_norm_rope_store_ex(int dtype, void* qkv, int tokens, int num_q, int num_kv, int head_dim,
+                                          const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                          const float* sin_t, int rotary_dim, int max_positions, const int* positions,
+                                          const int* slot_mapping, void* k_cache, void* v_cache, long long num_slots,
+                                          int* status, void* stream, int v_dim, int kv_in_row) {
+  return qk_norm_rope_store_impl(dtype, qkv, tokens, num_q, num_kv, head_dim, q_w, k_w, eps, cos_t, sin_t, rotary_dim,
+                                 max_positions, positions, kv_in_row ? slot_mapping : nullptr, k_cache, v_cache,
+                                 num_slots, status, stream, 0, v_dim, kv_in_row);
 }

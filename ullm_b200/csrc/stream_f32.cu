@@ -1,0 +1,189 @@
+// A residual stream kept in 32-bit whatever the engine's dtype, for
+// arrangements that norm a sub-layer's OUTPUT and add it to the stream:
+//
+//   embed_scaled      stream[t] = table[id[t]] * scale (+ sinusoid of the position), copy[t] = round(stream[t])
+//   norm_scale_add    stream[t] += mult * w * a[t] / sqrt(mean(a[t]^2) + eps),       copy[t] = round(stream[t])
+//   rmsnorm_rows_f32  out[r] = round(w * s / sqrt(mean(s^2) + eps)), s = stream[rows[r]]
+//   cast_rows_f32     copy = round(stream)
+//
+// `copy` is the stream rounded to the engine's dtype, the operand of the next
+// sub-layer's matrix products; with a 32-bit engine it is not needed (null).
+// Sums, norms, angles and the sinusoids are 32-bit; one rounding at each store.
+#include "common.cuh"
+
+// Position term: column c of position p is sin(p f_i) for even c and cos(p f_i) for odd c, i = c / 2, with
+// f_i = base^(-2 i / width) read from a 32-bit table the host built in 64-bit.  The angle is the 32-bit
+// product; sinf / cosf are the accurate forms (full range reduction).
+template <typename T, typename TAB>
+__global__ void embed_scaled_kernel(const int* __restrict__ ids, const TAB* __restrict__ table,
+                                    float* __restrict__ stream, T* __restrict__ copy, int hidden, int vocab,
+                                    float scale, const float* __restrict__ inv_freq,
+                                    const int* __restrict__ positions, const int* __restrict__ last_tokens,
+                                    const int* __restrict__ token_req, const int* __restrict__ req_slots,
+                                    int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 && last_tokens != nullptr) {
+    const int b = token_req[t];
+    id = b >= 0 ? last_tokens[req_slots[b]] : 0;
+  }
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0) ullm_report(status, ULLM_STATUS_TOKEN_ID, t, id);
+  const TAB* row = table + (long long)(bad ? 0 : id) * hidden;
+  const float p = inv_freq != nullptr ? (float)positions[t] : 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = bad ? 0.f : to_f32(row[c]) * scale;
+    if (inv_freq != nullptr) {
+      const float ang = p * inv_freq[c >> 1];
+      v += (c & 1) ? cosf(ang) : sinf(ang);
+    }
+    stream[(long long)t * hidden + c] = v;
+    if (copy != nullptr) copy[(long long)t * hidden + c] = from_f32<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void norm_scale_add_kernel(const T* __restrict__ a, float* __restrict__ stream,
+                                      const float* __restrict__ w, T* __restrict__ copy, int cols, float eps,
+                                      float mult) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long base = (long long)blockIdx.x * cols;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = to_f32(a[base + c]);
+    acc += v * v;
+  }
+  const float total = block_sum(acc, scratch);
+  const float rstd = 1.f / sqrtf(total / (float)cols + eps);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float s = stream[base + c] + mult * (to_f32(a[base + c]) * rstd * w[c]);
+    stream[base + c] = s;
+    if (copy != nullptr) copy[base + c] = from_f32<T>(s);
+  }
+}
+
+template <typename T>
+__global__ void rmsnorm_rows_f32_kernel(const float* __restrict__ stream, const int* __restrict__ rows,
+                                        const float* __restrict__ w, T* __restrict__ out, int cols, int src_rows,
+                                        float eps, int* status) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  int r = rows != nullptr ? rows[blockIdx.x] : (int)blockIdx.x;
+  const bool bad = r < 0 || r >= src_rows;
+  if (bad) {
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_ROW, blockIdx.x, r);
+    r = 0;
+  }
+  const float* s = stream + (long long)r * cols;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) acc += s[c] * s[c];
+  const float total = block_sum(acc, scratch);
+  const float rstd = 1.f / sqrtf(total / (float)cols + eps);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x)
+    out[(long long)blockIdx.x * cols + c] = from_f32<T>(bad ? 0.f : s[c] * rstd * w[c]);
+}
+
+template <typename T>
+__global__ void cast_rows_f32_kernel(const float* __restrict__ in, T* __restrict__ out, long long n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = from_f32<T>(in[i]);
+}
+
+static inline int row_threads(int cols) {
+  int threads = 32;
+  while (threads < 512 && threads * 4 < cols) threads <<= 1;
+  return threads;
+}
+
+template <typename T, typename TAB>
+static int embed_scaled_launch(const int* ids, const void* table, float* stream, void* copy, int tokens, int hidden,
+                               int vocab, float scale, const float* inv_freq, const int* positions,
+                               const int* last_tokens, const int* token_req, const int* req_slots, int* status,
+                               cudaStream_t st) {
+  return ullm_launch_kernel(embed_scaled_kernel<T, TAB>, dim3(tokens), dim3(row_threads(hidden)), 0, st, ids,
+                            (const TAB*)table, stream, (T*)copy, hidden, vocab, scale, inv_freq, positions,
+                            last_tokens, token_req, req_slots, status);
+}
+
+// `dtype`: the engine's dtype = the table's and the copy's.  `copy` may be null.
+extern "C" int ullm_embed_scaled(int dtype, const int* ids, const void* table, float* stream, void* copy, int tokens,
+                                 int hidden, int vocab, float scale, const float* inv_freq, const int* positions,
+                                 const int* last_tokens, const int* token_req, const int* req_slots, int* status,
+                                 void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (tokens < 0 || hidden <= 0 || vocab <= 0) return ULLM_ERR_BAD_SIZE;
+  if (inv_freq != nullptr && positions == nullptr) return ULLM_ERR_BAD_SIZE;
+  if (last_tokens != nullptr && (token_req == nullptr || req_slots == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  if (dtype == ULLM_DTYPE_F32)
+    return embed_scaled_launch<float, float>(ids, table, stream, copy, tokens, hidden, vocab, scale, inv_freq,
+                                             positions, last_tokens, token_req, req_slots, status, st);
+  if (dtype == ULLM_DTYPE_BF16)
+    return embed_scaled_launch<__nv_bfloat16, __nv_bfloat16>(ids, table, stream, copy, tokens, hidden, vocab, scale,
+                                                             inv_freq, positions, last_tokens, token_req, req_slots,
+                                                             status, st);
+  if (dtype == ULLM_DTYPE_F16)
+    return embed_scaled_launch<__half, __half>(ids, table, stream, copy, tokens, hidden, vocab, scale, inv_freq,
+                                               positions, last_tokens, token_req, req_slots, status, st);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_norm_scale_add(int dtype, const void* a, float* stream, const float* w, void* copy, int rows,
+                                   int cols, float eps, float mult, void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (rows < 0 || cols <= 0) return ULLM_ERR_BAD_SIZE;
+  if (rows == 0) return ULLM_OK;
+  const dim3 grid(rows), block(row_threads(cols));
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(norm_scale_add_kernel<float>, grid, block, 0, st, (const float*)a, stream, w,
+                              (float*)copy, cols, eps, mult);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(norm_scale_add_kernel<__nv_bfloat16>, grid, block, 0, st, (const __nv_bfloat16*)a,
+                              stream, w, (__nv_bfloat16*)copy, cols, eps, mult);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(norm_scale_add_kernel<__half>, grid, block, 0, st, (const __half*)a, stream, w,
+                              (__half*)copy, cols, eps, mult);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// `rows` may be null (row r of the output is row r of the stream).
+extern "C" int ullm_rmsnorm_rows_f32(int dtype, const float* stream, const int* rows, const float* w, void* out,
+                                     int count, int cols, int src_rows, float eps, int* status, void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (count < 0 || cols <= 0 || src_rows < 0) return ULLM_ERR_BAD_SIZE;
+  if (count == 0) return ULLM_OK;
+  const dim3 grid(count), block(row_threads(cols));
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(rmsnorm_rows_f32_kernel<float>, grid, block, 0, st, stream, rows, w, (float*)out, cols,
+                              src_rows, eps, status);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(rmsnorm_rows_f32_kernel<__nv_bfloat16>, grid, block, 0, st, stream, rows, w,
+                              (__nv_bfloat16*)out, cols, src_rows, eps, status);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(rmsnorm_rows_f32_kernel<__half>, grid, block, 0, st, stream, rows, w, (__half*)out,
+                              cols, src_rows, eps, status);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_cast_rows_f32(int dtype, const float* in, void* out, long long n, void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (n < 0) return ULLM_ERR_BAD_SIZE;
+  if (n == 0) return ULLM_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const dim3 grid((int)blocks), block(256);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(cast_rows_f32_kernel<__nv_bfloat16>, grid, block, 0, st, in, (__nv_bfloat16*)out, n);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(cast_rows_f32_kernel<__half>, grid, block, 0, st, in, (__half*)out, n);
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(cast_rows_f32_kernel<float>, grid, block, 0, st, in, (float*)out, n);
+  return ULLM_ERR_BAD_DTYPE;
+}

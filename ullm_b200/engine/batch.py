@@ -101,6 +101,9 @@ class StepContext:
     last_tokens: torch.Tensor | None = None  # int32 [request slots]: what each request sampled last (for id -1)
     # what a block prepared for the next block's first norm (norm object, operand r * w, sums of squares, eps)
     folded_norm: object = None
+    # a 32-bit residual stream rounded to the engine's dtype (the stream itself under a 32-bit engine): what the
+    # next sub-layer's matrix products read; whoever updates the stream leaves it here
+    stream_operand: object = None
     sum_kv_len: int = 0  # tokens all requests of the step hold after it, padding rows not counted
     num_live_requests: int = 0  # requests of the step without padding rows
 

@@ -38,7 +38,16 @@ class PagedAttention(Mixer):
         position=None,
         window: int | None = None,
         scale: float | None = None,
+        value_dim: int | None = None,
+        keep_first: int = 0,
+        own_kv: bool = True,
+        names: dict | None = None,
     ):
+        """`value_dim`: head size of the values and of the output (default: `head_dim`).  `window` with
+        `keep_first`: position i sees j <= i if i - j < window or j < keep_first.  `own_kv` False: the mixer has
+        no key / value projections (nor a key norm); it reads the cache of the execution the schedule names
+        (`ScheduleEntry.cache_of`) with queries, mask and scale of its own.  `names`: the checkpoint's names of
+        q, k, v, o, q_norm, k_norm behind the mixer's prefix (defaults: `q_proj.weight`, ..., `q_norm.`)."""
         super().__init__()
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
@@ -49,58 +58,73 @@ class PagedAttention(Mixer):
         self.qkv_bias = qkv_bias
         self.window = window
         self.scale = head_dim ** -0.5 if scale is None else scale
+        self.value_dim = head_dim if value_dim is None else value_dim
+        self.keep_first = int(keep_first)
+        self.own_kv = bool(own_kv)
+        if self.keep_first < 0 or self.value_dim <= 0:
+            raise ValueError("keep_first must not be negative and value_dim must be positive")
+        n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_bias="q_proj.bias",
+                 k_bias="k_proj.bias", v_bias="v_proj.bias", q_norm="q_norm.", k_norm="k_norm.")
+        n.update(names or {})
+        self.names = n
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
+        self.v_size = num_kv_heads * self.value_dim
+        self.o_size = num_heads * self.value_dim
         self.q_norm = build_norm(qk_norm) if qk_norm is not None else None
-        self.k_norm = build_norm(qk_norm) if qk_norm is not None else None
+        self.k_norm = build_norm(qk_norm) if (qk_norm is not None and self.own_kv) else None
         self.position = build_position_encoding(position) if position is not None else None
         check_attention_sizes(num_heads, num_kv_heads, head_dim, self.position.rotary_dim if self.position else 0)
 
     # -- parameters -------------------------------------------------------
     def param_decls(self):
-        H = self.hidden_size
-        d = {
-            "q_proj.weight": ParamDecl((self.q_size, H)),
-            "k_proj.weight": ParamDecl((self.kv_size, H)),
-            "v_proj.weight": ParamDecl((self.kv_size, H)),
-            "o_proj.weight": ParamDecl((H, self.q_size)),
-        }
+        H, n = self.hidden_size, self.names
+        d = {n["q"]: ParamDecl((self.q_size, H)), n["o"]: ParamDecl((H, self.o_size))}
+        if self.own_kv:
+            d[n["k"]] = ParamDecl((self.kv_size, H))
+            d[n["v"]] = ParamDecl((self.v_size, H))
         if self.qkv_bias:
-            d["q_proj.bias"] = ParamDecl((self.q_size,), "bias")
-            d["k_proj.bias"] = ParamDecl((self.kv_size,), "bias")
-            d["v_proj.bias"] = ParamDecl((self.kv_size,), "bias")
+            d[n["q_bias"]] = ParamDecl((self.q_size,), "bias")
+            if self.own_kv:
+                d[n["k_bias"]] = ParamDecl((self.kv_size,), "bias")
+                d[n["v_bias"]] = ParamDecl((self.v_size,), "bias")
         return d
 
     def subparts(self):
         s = {}
         if self.q_norm is not None:
-            s["q_norm."] = self.q_norm
-            s["k_norm."] = self.k_norm
+            s[self.names["q_norm"]] = self.q_norm
+        if self.k_norm is not None:
+            s[self.names["k_norm"]] = self.k_norm
         return s
 
     def materialize(self, make):
-        H, q, kv = self.hidden_size, self.q_size, self.kv_size
-        self.w_qkv = make("qkv_proj.weight", ParamDecl((q + 2 * kv, H)))
-        self.tensors["q_proj.weight"] = self.w_qkv[:q]
-        self.tensors["k_proj.weight"] = self.w_qkv[q:q + kv]
-        self.tensors["v_proj.weight"] = self.w_qkv[q + kv:]
-        self.tensors["o_proj.weight"] = make("o_proj.weight", ParamDecl((H, q)))
+        H, q, kv, n = self.hidden_size, self.q_size, self.kv_size, self.names
+        rows = q + ((kv + self.v_size) if self.own_kv else 0)
+        self.w_qkv = make("qkv_proj.weight", ParamDecl((rows, H)))
+        self.tensors[n["q"]] = self.w_qkv[:q]
+        if self.own_kv:
+            self.tensors[n["k"]] = self.w_qkv[q:q + kv]
+            self.tensors[n["v"]] = self.w_qkv[q + kv:]
+        self.tensors[n["o"]] = make("o_proj.weight", ParamDecl((H, self.o_size)))
         self.b_qkv = None
         if self.qkv_bias:
-            self.b_qkv = make("qkv_proj.bias", ParamDecl((q + 2 * kv,), "bias"))
-            self.tensors["q_proj.bias"] = self.b_qkv[:q]
-            self.tensors["k_proj.bias"] = self.b_qkv[q:q + kv]
-            self.tensors["v_proj.bias"] = self.b_qkv[q + kv:]
+            self.b_qkv = make("qkv_proj.bias", ParamDecl((rows,), "bias"))
+            self.tensors[n["q_bias"]] = self.b_qkv[:q]
+            if self.own_kv:
+                self.tensors[n["k_bias"]] = self.b_qkv[q:q + kv]
+                self.tensors[n["v_bias"]] = self.b_qkv[q + kv:]
         if self.position is not None:
             self.position.build_tables(self.w_qkv.device)
 
     # -- cache ------------------------------------------------------------
     def cache_need(self):
-        return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
+        return CacheNeed(self.num_kv_heads, self.head_dim, self.window,
+                         None if self.value_dim == self.head_dim else self.value_dim, self.keep_first if self.window else 0)
 
     def activation_elems(self):
         # qkv, the attention's output, the projected output
-        return self.q_size + 2 * self.kv_size + self.q_size + self.hidden_size
+        return self.q_size + self.kv_size + self.v_size + self.o_size + self.hidden_size
 
     # -- which kernels a decode step takes ---------------------------------
     def graph_key(self, ctx):
@@ -114,7 +138,7 @@ class PagedAttention(Mixer):
         return bool(ctx.decode_only and is_ragged(ctx.num_live_requests, ctx.max_kv_len, ctx.sum_kv_len))
 
     def output_projection(self):
-        return self.tensors["o_proj.weight"], None
+        return self.tensors[self.names["o"]], None
 
     def takes_input_norm(self):
         return True
@@ -124,7 +148,11 @@ class PagedAttention(Mixer):
         K = kernels()
         T = x.shape[0]
         ragged = self._ragged(ctx)
-        qkv = ctx.workspace.tokens("attn.qkv", T, self.q_size + 2 * self.kv_size, x.dtype)
+        if not self.own_kv and cache.writes:
+            raise RuntimeError("a mixer without key / value projections must read another execution's cache "
+                               "(ScheduleEntry.cache_of)")
+        plain = self.own_kv and self.value_dim == self.head_dim and self.keep_first == 0
+        qkv = ctx.workspace.tokens("attn.qkv", T, self.w_qkv.shape[0], x.dtype)
         if input_norm is not None:
             # x is r * w: the projection multiplies its sums by the rows' 1 / rms (a norm folded in front of it)
             if not K.stream_linear(x, self.w_qkv, qkv, self.b_qkv, norm_in_front=input_norm):
@@ -133,13 +161,23 @@ class PagedAttention(Mixer):
             linear(x, self.w_qkv, qkv, self.b_qkv)
         g = cache.group
         tables = self.position.tables() if self.position is not None else {}
-        q_w = self.q_norm.tensors["weight"] if self.q_norm is not None else None
-        k_w = self.k_norm.tensors["weight"] if self.k_norm is not None else None
+        q_w = self.q_norm.weight if self.q_norm is not None else None
+        k_w = self.k_norm.weight if self.k_norm is not None else None
         eps = self.q_norm.eps if self.q_norm is not None else 0.0
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         slot_mapping = g.slot_mapping if cache.writes else None
         fuse = None
-        if self.position is not None and self.position.transforms_qk():
+        if not plain:
+            # values of a head size of their own, kept first positions or borrowed keys and values: the general
+            # kernels (norm / rotation / page write, then attention), in prompt and decode steps alike
+            if self.position is not None and self.position.transforms_qk():
+                raise NotImplementedError("a position encoding with code of its own beside these attention options")
+            K.qk_norm_rope_store(
+                qkv, self.num_heads, self.num_kv_heads, self.head_dim, q_w, k_w, eps, tables.get("cos"),
+                tables.get("sin"), rotary_dim, ctx.positions, slot_mapping, cache.k_pages, cache.v_pages,
+                v_dim=self.value_dim, kv_in_row=self.own_kv,
+            )
+        elif self.position is not None and self.position.transforms_qk():
             # an encoding with code of its own: norm q and k, let it change them, then store the keys and values
             if q_w is not None or k_w is not None:
                 K.qk_norm_in_place(qkv, self.num_heads, self.num_kv_heads, self.head_dim, q_w, k_w, eps)
@@ -159,15 +197,16 @@ class PagedAttention(Mixer):
                 qkv, self.num_heads, self.num_kv_heads, self.head_dim, q_w, k_w, eps, tables.get("cos"),
                 tables.get("sin"), rotary_dim, ctx.positions, slot_mapping, cache.k_pages, cache.v_pages,
             )
-        attn = ctx.workspace.tokens("attn.out", T, self.q_size, x.dtype)
+        attn = ctx.workspace.tokens("attn.out", T, self.o_size, x.dtype)
         K.paged_attention(
             qkv, attn, cache.k_pages, cache.v_pages, g.block_table, g.req_slots, ctx.cu_q, g.kv_len,
             ctx.token_req,
             self.num_heads, self.num_kv_heads, self.head_dim, g.page_size,
             self.window or 0, self.scale, ctx, ragged=ragged, **({"fuse": fuse} if fuse is not None else {}),
+            **({} if plain else {"v_dim": self.value_dim, "keep_first": self.keep_first if self.window else 0}),
         )
         if not project_output:
             return attn  # (the caller multiplies by `output_projection()` itself)
         out = ctx.workspace.tokens("mixer.out", T, self.hidden_size, x.dtype)
-        linear(attn, self.tensors["o_proj.weight"], out)
+        linear(attn, self.tensors[self.names["o"]], out)
         return out

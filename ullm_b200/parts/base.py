@@ -35,7 +35,8 @@ class ParamDecl:
     """A parameter as the checkpoint stores it.  `role` decides precision and
     random init: "matrix" (embedding and linear weights: engine dtype, N(0,
     std)), "bias" (engine dtype, N(0, std)), "norm" (always held in 32-bit,
-    1 + N(0, norm_std))."""
+    1 + N(0, norm_std)), "bias32" (a bias that enters 32-bit arithmetic: always
+    held in 32-bit, N(0, std))."""
 
     shape: tuple[int, ...]
     role: str = "matrix"
@@ -44,11 +45,19 @@ class ParamDecl:
 @dataclass(frozen=True)
 class CacheNeed:
     """Keys and values this mixer keeps per token: `num_kv_heads` x `head_dim`
-    for K and for V.  `window`: None keeps every token, w keeps the last w."""
+    for K and `num_kv_heads` x `value_dim` for V (None: `head_dim`).  `window`:
+    None keeps every token, w keeps the last w, and with `keep_first` also the
+    first `keep_first` tokens of the request."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+    keep_first: int = 0
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -104,6 +113,15 @@ class Part:
 
 class Norm(Part):
     def forward(self, x, residual=None, out=None):
+        raise NotImplementedError
+
+    def scale_add(self, a, stream, mult: float, copy=None):
+        """stream (32-bit, in place) += mult * norm(a); `copy`, if given, receives the stream rounded to a's dtype.
+        For arrangements that norm a sub-layer's output."""
+        raise NotImplementedError
+
+    def forward_rows(self, stream, rows, out):
+        """out[r] = norm(stream[rows[r]]) for a 32-bit stream (`rows` None: every row), rounded to out's dtype."""
         raise NotImplementedError
 
     def rms_params(self):
@@ -164,6 +182,13 @@ class Mixer(Part):
         front of it (`forward(..., project_output=False)` then returns its [T, width] input); None otherwise.
         A block may fold that product into a fused kernel."""
         return None
+
+    def operand_dtype(self):
+        """The dtype of the rows this mixer's `forward` takes (that of its first matrix)."""
+        for t in self.all_tensors().values():
+            if t.dim() >= 2:
+                return t.dtype
+        raise RuntimeError("this mixer has no matrix to read its operand's dtype from")
 
     def forward(self, x, ctx, cache):
         raise NotImplementedError

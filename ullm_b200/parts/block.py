@@ -146,3 +146,65 @@ class PreNormResidualBlock(Block):
         if not kernels().layer_tail_applies(rows, residual.dtype, residual.shape[1], w_o.shape[1], w_down.shape[1]):
             return None
         return w_o, norm_w, eps, w_gate_up, w_down, act
+
+
+@register_block("outnorm_residual")
+class OutputNormResidualBlock(Block):
+    """The norm sits on each sub-layer's OUTPUT, and the normed output is added to the stream with a multiplier:
+
+        x <- x + mult * norm_a(mixer(x));   x <- x + mult * norm_b(feed_forward(x))
+
+    Both sub-layers read the stream itself.  The stream is 32-bit whatever the engine's dtype (the model is built
+    with `stream_dtype="float32"`); the sub-layers' operand is the stream rounded to the engine's dtype, which the
+    kernel that updates the stream writes beside it (`ctx.stream_operand`).  A layer may have no feed-forward."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, names=None, residual_mult: float = 1.0):
+        super().__init__()
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm come together or not at all")
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+        self.residual_mult = float(residual_mult)
+        n = names or {}
+        self.names = {
+            "mixer": n.get("mixer", "mixer."),
+            "feed_forward": n.get("feed_forward", "feed_forward."),
+            "mixer_norm": n.get("mixer_norm", "mixer_norm."),
+            "feed_forward_norm": n.get("feed_forward_norm", "feed_forward_norm."),
+        }
+
+    def subparts(self):
+        s = {self.names["mixer_norm"]: self.mixer_norm, self.names["mixer"]: self.mixer}
+        if self.feed_forward is not None:
+            s[self.names["feed_forward_norm"]] = self.feed_forward_norm
+            s[self.names["feed_forward"]] = self.feed_forward
+        return s
+
+    def activation_elems(self):
+        ff = self.feed_forward.activation_elems() if self.feed_forward is not None else 0
+        return 3 * getattr(self.mixer_norm, "size", 0) + max(self.mixer.activation_elems(), ff)
+
+    def forward(self, x, residual, ctx, cache):
+        """The stream arrives as `x` (first block, residual None) or as `residual` (x None); returns (None, stream)."""
+        stream = residual if residual is not None else x
+        if stream.dtype != torch.float32:
+            raise RuntimeError("this block takes a 32-bit residual stream (ModelSpec.stream_dtype='float32')")
+        T, H = stream.shape
+        h = ctx.stream_operand
+        if h is None or h.shape != stream.shape:
+            engine_dtype = self.mixer.operand_dtype()
+            if engine_dtype == torch.float32:
+                h = stream
+            else:
+                h = ctx.workspace.tokens("model.stream_copy", T, H, engine_dtype)
+                kernels().cast_rows_f32(stream, h)
+        copy = None if h is stream else h
+        a = self.mixer.forward(h, ctx, cache)
+        self.mixer_norm.scale_add(a, stream, self.residual_mult, copy)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(h, ctx)
+            self.feed_forward_norm.scale_add(y, stream, self.residual_mult, copy)
+        ctx.stream_operand = h
+        return None, stream

@@ -10,21 +10,49 @@ from .base import ParamDecl, Part
 
 
 class TokenEmbedding(Part):
-    def __init__(self, vocab_size: int, hidden_size: int):
+    """`scale` multiplies the gathered row; `position`, an encoding that `adds_to_embedding()`, is added to it;
+    `param` is the table's name behind the part's prefix.  With either, or with a 32-bit stream under a 16-bit
+    engine, `forward_stream` is the form to call: it writes the 32-bit stream and its rounded copy."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, position=None, param: str = "weight"):
         super().__init__()
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
+        self.scale = float(scale)
+        self.position = position
+        self.param = param
 
     def param_decls(self):
-        return {"weight": ParamDecl((self.vocab_size, self.hidden_size))}
+        return {self.param: ParamDecl((self.vocab_size, self.hidden_size))}
+
+    @property
+    def table(self):
+        return self.tensors[self.param]
+
+    def materialize(self, make):
+        super().materialize(make)
+        if self.position is not None:
+            self.position.build_tables(self.table.device)
+
+    def plain(self) -> bool:
+        return self.scale == 1.0 and self.position is None
+
+    def forward_stream(self, token_ids, stream, copy, ctx):
+        """stream [T, hidden] float32 = table[id] * scale (+ the added position encoding); copy (the table's dtype,
+        or None) = the rounded stream."""
+        inv = self.position.tables()["inv_freq"] if self.position is not None else None
+        kernels().embed_scaled(token_ids, self.table, stream, copy, self.scale, inv, ctx.positions if inv is not None else None,
+                               ctx.last_tokens, ctx.token_req if ctx.last_tokens is not None else None,
+                               ctx.req_slots if ctx.last_tokens is not None else None)
+        return stream
 
     def forward(self, token_ids, out, ctx=None):
         """An id of -1 stands for the token its request sampled last, when the step's context carries the
         device array that holds those (`ctx.last_tokens`)."""
         if ctx is not None and ctx.last_tokens is not None:
-            kernels().embedding(token_ids, self.tensors["weight"], out, ctx.last_tokens, ctx.token_req, ctx.req_slots)
+            kernels().embedding(token_ids, self.table, out, ctx.last_tokens, ctx.token_req, ctx.req_slots)
         else:
-            kernels().embedding(token_ids, self.tensors["weight"], out)
+            kernels().embedding(token_ids, self.table, out)
         return out
 
 
@@ -32,19 +60,20 @@ class OutputHead(Part):
     """logits = h W^T in 32-bit output.  `tied_to`, when set, is the embedding
     part whose table is read and no tensor of its own is declared."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None, param: str = "weight"):
         super().__init__()
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
+        self.param = param
 
     def param_decls(self):
         if self.tied_to is not None:
             return {}
-        return {"weight": ParamDecl((self.vocab_size, self.hidden_size))}
+        return {self.param: ParamDecl((self.vocab_size, self.hidden_size))}
 
     def weight(self):
-        return self.tied_to.tensors["weight"] if self.tied_to is not None else self.tensors["weight"]
+        return self.tied_to.table if self.tied_to is not None else self.tensors[self.param]
 
     def forward(self, h, out_f32):
         kernels().linear_f32_out(h, self.weight(), out_f32)

@@ -14,7 +14,7 @@ from ..config.specs import ModelSpec
 from ..csrc import kernels
 from .base import Part
 from .embedding import OutputHead, TokenEmbedding
-from .registry import build_block, build_norm
+from .registry import build_block, build_norm, build_position_encoding
 
 
 class DecoderModel(Part):
@@ -22,11 +22,22 @@ class DecoderModel(Part):
         super().__init__()
         spec.validate()
         self.spec = spec
-        self.embedding = TokenEmbedding(spec.vocab_size, spec.hidden_size)
+        position = None
+        if spec.embedding_position is not None:
+            position = build_position_encoding(spec.embedding_position)
+            if not getattr(position, "adds_to_embedding", lambda: False)():
+                raise ValueError(f"position encoding {spec.embedding_position.kind!r} cannot be added to an embedding")
+        self.embedding = TokenEmbedding(spec.vocab_size, spec.hidden_size, spec.embedding_scale, position,
+                                        spec.embedding_param)
+        if spec.stream_dtype not in ("engine", "float32"):
+            raise ValueError(f"stream_dtype {spec.stream_dtype!r}: 'engine' or 'float32'")
+        self.stream_f32 = spec.stream_dtype == "float32"
+        if not self.stream_f32 and not self.embedding.plain():
+            raise ValueError("a scaled embedding or an added position encoding needs stream_dtype='float32'")
         self.blocks = [build_block(ls) for ls in spec.layers]
         self.final_norm = build_norm(spec.final_norm)
         tied = spec.tie_embeddings and not untie_head
-        self.head = OutputHead(spec.vocab_size, spec.hidden_size, self.embedding if tied else None)
+        self.head = OutputHead(spec.vocab_size, spec.hidden_size, self.embedding if tied else None, spec.head_param)
         self.schedule = list(spec.schedule)
         # one mixer of each group answers `graph_key` for all of its kind
         seen: dict = {}
@@ -66,7 +77,7 @@ class DecoderModel(Part):
         self.device = torch.device(device)
 
         def make(name, decl):
-            dt = torch.float32 if decl.role == "norm" else dtype
+            dt = torch.float32 if decl.role in ("norm", "bias32") else dtype
             return torch.empty(decl.shape, dtype=dt, device=self.device)
 
         self.materialize_all(make)
@@ -76,8 +87,18 @@ class DecoderModel(Part):
         """Runs the blocks over the step's tokens.  Returns (y, residual): what the last block left to be added
         (or None) and the residual stream, before the final norm."""
         T = ctx.num_tokens
-        x = ctx.workspace.tokens("model.hidden", T, self.spec.hidden_size, self.dtype)
-        self.embedding.forward(ctx.token_ids, x, ctx)
+        ctx.stream_operand = None
+        if self.stream_f32:
+            # the stream is 32-bit; its copy rounded to the engine's dtype is the first sub-layer's operand
+            x = ctx.workspace.tokens("model.stream", T, self.spec.hidden_size, torch.float32)
+            copy = None
+            if self.dtype != torch.float32:
+                copy = ctx.workspace.tokens("model.stream_copy", T, self.spec.hidden_size, self.dtype)
+            self.embedding.forward_stream(ctx.token_ids, x, copy, ctx)
+            ctx.stream_operand = copy if copy is not None else x
+        else:
+            x = ctx.workspace.tokens("model.hidden", T, self.spec.hidden_size, self.dtype)
+            self.embedding.forward(ctx.token_ids, x, ctx)
         residual = None
         n = len(self.schedule)
         for i, e in enumerate(self.schedule):
@@ -101,7 +122,11 @@ class DecoderModel(Part):
         K = kernels()
         H = self.spec.hidden_size
         ys = ctx.workspace.requests("head.y", R, H, self.dtype)
-        if y is None or residual is None:
+        if self.stream_f32:
+            if y is not None and residual is not None:
+                raise RuntimeError("a block of a 32-bit stream left something pending beside the stream")
+            self.final_norm.forward_rows(residual if residual is not None else y, ctx.logits_rows, ys)
+        elif y is None or residual is None:
             # nothing is pending beside the stream (a block that adds its own output), or there is no stream
             K.gather_rows(y if residual is None else residual, ctx.logits_rows, ys)
             self.final_norm.forward(ys, None, out=ys)

@@ -14,16 +14,30 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, param: str = "weight"):
+        """`param`: the name of the weight behind the norm's prefix (may be empty: the prefix is the name)."""
         super().__init__()
         self.size = size
         self.eps = eps
+        self.param = param
 
     def param_decls(self):
-        return {"weight": ParamDecl((self.size,), "norm")}
+        return {self.param: ParamDecl((self.size,), "norm")}
+
+    @property
+    def weight(self):
+        return self.tensors[self.param]
 
     def rms_params(self):
-        return self.tensors["weight"], self.eps
+        return self.weight, self.eps
+
+    def scale_add(self, a, stream, mult: float, copy=None):
+        kernels().norm_scale_add(a, stream, self.weight, self.eps, mult, copy)
+        return stream
+
+    def forward_rows(self, stream, rows, out):
+        kernels().rmsnorm_rows_f32(stream, rows, self.weight, self.eps, out)
+        return out
 
     def forward(self, x, residual=None, out=None):
         """x [T, size].  residual (same shape), if given, is updated in place
@@ -31,5 +45,5 @@ class RMSNorm(Norm):
         may be `x`)."""
         if out is None:
             out = x
-        kernels().add_rmsnorm(x, residual, self.tensors["weight"], self.eps, out)
+        kernels().add_rmsnorm(x, residual, self.weight, self.eps, out)
         return out

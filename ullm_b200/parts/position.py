@@ -50,3 +50,32 @@ class NoPositions(PositionEncoding):
 
     def build_tables(self, device) -> None:
         pass
+
+
+@register_position_encoding("sinusoid_added")
+class AddedSinusoid(PositionEncoding):
+    """An absolute encoding that is ADDED to the token embedding, not applied to queries and keys: column 2i of
+    position p is sin(p f_i), column 2i + 1 is cos(p f_i), f_i = theta^(-2i / width).  `rotary_dim` is the width of
+    the embedding.  The table of the f_i is built in 64-bit and kept in 32-bit; the embedding kernel forms the
+    32-bit angle and the sinusoids itself, so there is no table per position and no largest position."""
+
+    def __init__(self, rotary_dim: int, theta: float = 10000.0, max_positions: int = 0):
+        super().__init__()
+        if rotary_dim <= 0:
+            raise ValueError("the width of an added encoding must be positive")
+        self.width = rotary_dim
+        self.rotary_dim = 0  # nothing is rotated
+        self.theta = float(theta)
+        self.max_positions = max_positions
+        self._tables: dict[str, torch.Tensor] = {}
+
+    def adds_to_embedding(self) -> bool:
+        return True
+
+    def build_tables(self, device) -> None:
+        i = torch.arange((self.width + 1) // 2, dtype=torch.float64)
+        inv = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.width)
+        self._tables = {"inv_freq": inv.to(torch.float32).contiguous().to(device)}
+
+    def tables(self):
+        return self._tables

@@ -41,7 +41,7 @@ def _lookup(table: dict[str, type], what: str, kind: str) -> type:
 
 
 def build_norm(spec):
-    return _lookup(NORMS, "norm", spec.kind)(size=spec.size, eps=spec.eps)
+    return _lookup(NORMS, "norm", spec.kind)(size=spec.size, eps=spec.eps, **spec.args)
 
 
 def build_position_encoding(spec):
@@ -62,8 +62,9 @@ def build_block(layer_spec):
     cls = _lookup(BLOCKS, "block", layer_spec.block)
     return cls(
         mixer=build_mixer(layer_spec.mixer),
-        feed_forward=build_feed_forward(layer_spec.feed_forward),
+        feed_forward=build_feed_forward(layer_spec.feed_forward) if layer_spec.feed_forward is not None else None,
         mixer_norm=build_norm(layer_spec.mixer_norm),
-        feed_forward_norm=build_norm(layer_spec.feed_forward_norm),
+        feed_forward_norm=build_norm(layer_spec.feed_forward_norm) if layer_spec.feed_forward_norm is not None else None,
         names=layer_spec.names,
+        **layer_spec.block_args,
     )
