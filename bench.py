@@ -508,6 +508,174 @@ def run_long_context(args) -> dict:
             "decode_b8_frac": round(decode_bytes(nums, B, ctx, cfg["hidden_size"]) / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
 
 
+# ---------------------------------------------------------------------------------------------------------
+# `--workload ludalix`: the Ludalix decoder beside the Qwen3 dense decoder at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------
+def ludalix_config(width: int, heads: int, kv_heads: int, ff: int, experts: int, top: int, expert_ff: int, window: int,
+                   keep_first: int, state_heads: int, state_dim: int, state_vdim: int, groups: int, vocab: int) -> dict:
+    """`groups` times four layers: state + dense, attention + experts, attention on the layer before's keys and
+    values + experts, state + experts."""
+    att = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, mask=dict(size=window, keep_first=keep_first),
+               scale=128 ** -0.5)
+    st = dict(heads=state_heads, dim=state_dim, vdim=state_vdim, gate_cap=15.0)
+    moe = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top))
+    layers = []
+    for g in range(groups):
+        layers += [dict(type="mlstm", mixer=dict(st), mlp=dict(kind="dense", ff=ff, limit=7.0)),
+                   dict(type="attention", mixer=dict(att), mlp=dict(moe)),
+                   dict(type="attention", mixer=dict(att, kv_from=4 * g + 1), mlp=dict(moe)),
+                   dict(type="mlstm", mixer=dict(st), mlp=dict(moe))]
+    return dict(architecture="Ludalix", vocab=vocab, width=width, residual_mult=0.7, embedding=dict(scale=16.0),
+                norm=dict(eps=1e-5), layers=layers, torch_dtype="bfloat16")
+
+
+LUDALIX_SIZES = {
+    # name: (Ludalix arguments, the Qwen3 configuration of equal width, heads, dense feed-forward and depth)
+    "w2048": (dict(width=2048, heads=16, kv_heads=4, ff=8192, experts=16, top=2, expert_ff=1024, window=1024,
+                   keep_first=4, state_heads=8, state_dim=128, state_vdim=256, groups=2, vocab=32768),
+              dict(QWEN3_8B, num_hidden_layers=8, hidden_size=2048, num_attention_heads=16, num_key_value_heads=4,
+                   intermediate_size=8192, vocab_size=32768)),
+    "w4096": (dict(width=4096, heads=32, kv_heads=8, ff=12288, experts=32, top=2, expert_ff=2048, window=2048,
+                   keep_first=4, state_heads=8, state_dim=256, state_vdim=512, groups=2, vocab=32768),
+              dict(QWEN3_8B, num_hidden_layers=8, vocab_size=32768)),
+}
+
+
+def _group_times(runner, entries_fn, repeats: int = 3) -> dict:
+    """Per kernel group: microseconds of one eager step (median over `repeats` steps made by `entries_fn`)."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine.profiler import KernelGroupTimer
+
+    K = kernels()
+    runs = []
+    for i in range(repeats + 1):
+        entries, after = entries_fn(i)
+        timer = KernelGroupTimer()
+        K.timer = timer
+        try:
+            runner.step(entries)
+            torch.cuda.synchronize()
+        finally:
+            K.timer = None
+        after()
+        if i:
+            runs.append(timer.totals())
+    out = {}
+    for g in sorted({g for r in runs for g in r}):
+        out[g] = {"us": round(statistics.median(r.get(g, {"us": 0.0})["us"] for r in runs), 1),
+                  "calls": runs[0].get(g, {"calls": 0})["calls"]}
+    return out
+
+
+def _measure_model(cfg: dict, layers_key: bool, T: int, B: int, ctx_len: int, steps: int, warm: int) -> dict:
+    """Prefill of one T-token prompt and decode steps of B requests holding ctx_len tokens, through the engine
+    (decode from CUDA graphs); then the kernel groups of one eager prefill step and one eager decode step."""
+    import torch
+
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine import StepEntry
+    from ullm_b200.sampling import SamplingParams
+
+    per_req = ctx_len + 2 * (steps + warm) + 64
+    layers = cfg.get("num_hidden_layers", 0)
+    llm, _ = _make_llm(cfg, layers, B, (B + 2) * (-(-per_req // PAGE_SIZE)) + 64, budget=T, context=ctx_len + 1024)
+    eng = llm.engine
+    vocab = eng.runner.spec.vocab_size
+    g = torch.Generator().manual_seed(2)
+
+    def prompt(n):
+        return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+    def drain():
+        while eng.has_unfinished_sequences():
+            eng.step()
+
+    pre_ms = []
+    for i in range(4):
+        eng.add_sequence(f"p{i}", prompt(T), SamplingParams(temperature=0.0, ignore_eos=True, max_new_tokens=1))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        drain()
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms.append(e0.elapsed_time(e1))
+    pre = statistics.median(pre_ms[1:])
+    sp = SamplingParams(temperature=0.0, ignore_eos=True, max_new_tokens=10**9)
+    ids = [f"d{i}" for i in range(B)]
+    for sid in ids:
+        eng.add_sequence(sid, prompt(ctx_len), sp)
+    while any(s.num_pending > 1 or s.status.name == "WAITING" for s in [eng.scheduler.get_sequence(i) for i in ids]):
+        eng.step()
+    for _ in range(warm):
+        eng.step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        eng.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    for sid in ids:
+        eng.abort_sequence(sid)
+    drain()
+    kernels().raise_on_status()
+    # kernel groups, eagerly, on the same runner
+    r = eng.runner
+
+    def prefill_entries(i):
+        rid = f"gp{i}"
+        r.add_request(rid)
+        return [StepEntry(rid, prompt(T), [T - 1])], (lambda: r.end_request(rid))
+
+    groups_prefill = _group_times(r, prefill_entries)
+    rids = [f"gd{i}" for i in range(B)]
+    for rid in rids:
+        r.add_request(rid)
+        r.step([StepEntry(rid, prompt(ctx_len), [])])
+
+    def decode_entries(i):
+        return [StepEntry(rid, prompt(1), [0]) for rid in rids], (lambda: None)
+
+    groups_decode = _group_times(r, decode_entries)
+    for rid in rids:
+        r.end_request(rid)
+    kernels().raise_on_status()
+    weights = sum(t.numel() * t.element_size() for t in {t.data_ptr(): t for t in r.model.all_tensors().values()}.values())
+    del llm, eng
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    return {"prefill_ms": round(pre, 3), "prefill_tok_s": round(T / (pre / 1e3), 1), "decode_ms": round(ms, 4),
+            "decode_tok_s": round(B / (ms / 1e3), 1), "weight_bytes": int(weights),
+            "groups_prefill_us": groups_prefill, "groups_decode_us": groups_decode}
+
+
+def run_ludalix(args) -> dict:
+    """`--workload ludalix`: prefill (one prompt of 2,048 tokens) and decode (8 requests holding 2,048 tokens each)
+    of the Ludalix decoder at layer sizes that resemble a real model's, random weights, beside the Qwen3 dense
+    decoder of equal width, heads, dense feed-forward and depth; per kernel group the device time of one eager
+    step of each kind.  One JSON object; the default workload and its line are untouched."""
+    T, B, ctx_len = PREFILL_TOKENS, args.batch, START_CONTEXT
+    out = {"workload": "ludalix", "prefill_tokens": T, "decode_batch": B, "decode_context": ctx_len,
+           "data": "synthetic", "dtype": "bf16", "peaks": peaks(), "sizes": {}}
+    names = [args.case] if args.case else list(LUDALIX_SIZES)
+    for name in names:
+        lud_args, qwen = LUDALIX_SIZES[name]
+        lud = ludalix_config(**lud_args)
+        out["sizes"][name] = {
+            "ludalix": dict(_measure_model(lud, False, T, B, ctx_len, args.steps, args.warmup), layers=len(lud["layers"])),
+            "qwen3_dense": dict(_measure_model(dict(qwen), True, T, B, ctx_len, args.steps, args.warmup),
+                                layers=qwen["num_hidden_layers"]),
+        }
+    return out
+
+
+
 def run_extra_shapes(args, impl: str) -> dict:
     """The two further workloads, each in a process of its own (the 32B shape needs the device to itself), as
     flat entries for `points`."""
@@ -1170,7 +1338,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long", "ludalix"],
                     help="8b: the default line (Qwen3-8B layer sizes); 32b: the same at Qwen3-32B layer sizes; "
                          "serve-0.6b: 256 requests under continuous batching at Qwen3-0.6B layer sizes; 8b-long: "
                          "prefill of 16,384 tokens and decode of 8 requests at that context")
@@ -1219,6 +1387,9 @@ def main() -> int:
         return 1
     if args.workload == "8b-long":
         print(json.dumps(run_long_context(args)))
+        return 0
+    if args.workload == "ludalix":
+        print(json.dumps(run_ludalix(args)))
         return 0
     out = run_serve(args) if args.workload == "serve-0.6b" else run_ours(args)
     if extra:

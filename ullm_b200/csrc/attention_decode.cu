@@ -45,6 +45,7 @@ struct DecFuse {
   long long num_slots;
   int max_positions;
   float eps;
+  int keep_first;  // with a window: the positions below it stay visible (0: none)
 };
 
 // 2^x by the hardware's unit alone (exp2f adds a range fix-up around the same instruction)
@@ -77,13 +78,17 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
   const int kvl = kv_len[b];
   const int pos = kvl - 1;
   const int lo = (window > 0 && pos >= 0) ? max(0, pos - window + 1) : 0;
-  const int n_keys = pos >= 0 ? pos - lo + 1 : 0;
+  // The keys a row sees are numbered 0 .. n_keys - 1: first the kept first positions that the window has left
+  // behind (0 .. kept - 1), then the window (lo .. pos).  Blocks and warps split this numbering; only the page
+  // lookup needs the position itself.
+  const int kept = min(fu.keep_first, lo);
+  const int n_keys = pos >= 0 ? kept + pos - lo + 1 : 0;
   // this block's keys, then this warp's keys (both in whole tiles, except the last)
   int per_split = (n_keys + num_splits - 1) / num_splits;
   per_split = (per_split + DEC_TILE * DEC_WARPS - 1) / (DEC_TILE * DEC_WARPS) * (DEC_TILE * DEC_WARPS);
   const int s_begin = min(n_keys, split * per_split), s_end = min(n_keys, s_begin + per_split);
   const int per_warp = per_split / DEC_WARPS;
-  const int w_begin = lo + min(s_end, s_begin + warp * per_warp), w_end = lo + min(s_end, s_begin + (warp + 1) * per_warp);
+  const int w_begin = min(s_end, s_begin + warp * per_warp), w_end = min(s_end, s_begin + (warp + 1) * per_warp);
   const int tiles = (w_end - w_begin + DEC_TILE - 1) / DEC_TILE;
   const int* bt = block_table + (long long)req_slots[b] * max_pages;
   const long long kv_row = (long long)num_kv * D;
@@ -96,8 +101,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     // lanes 0..15 look up the slot of row `lane`
     long long my_slot = -1;
     if (lane < DEC_TILE) {
-      const int key = base + lane;
-      if (key < w_end) {
+      if (base + lane < w_end) {
+        const int key = base + lane < kept ? base + lane : lo + (base + lane - kept);
         const int page = bt[key / page_size];
         if (page < 0 || page >= num_pages) ullm_report(status, ULLM_STATUS_PAGE, b, page);
         else my_slot = (long long)page * page_size + key % page_size;
@@ -224,7 +229,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
     // ---- the new key and value: the warp whose keys end with the newest one prepares them, writes them to the
     // cache for the steps to come, and keeps them to put them into its own last tile once that has landed (what
     // the tile's load finds in the slot meanwhile does not matter) ----------------------------------------------
-    if (fu.slot_mapping != nullptr && n_keys > 0 && w_end == lo + n_keys && w_end > w_begin) {
+    if (fu.slot_mapping != nullptr && n_keys > 0 && w_end == n_keys && w_end > w_begin) {
       constexpr int LW = D / 8;  // lanes of a row
       long long slot = fu.slot_mapping[b];
       if (slot >= fu.num_slots) {
@@ -627,6 +632,21 @@ extern "C" int ullm_decode_attention(const void* q, long long q_row_stride, cons
                                stream, fu);
 }
 
+// With a window that keeps the first `keep_first` positions of every request visible.
+extern "C" int ullm_decode_attention_kept(const void* q, long long q_row_stride, const void* k_cache,
+                                          const void* v_cache, const int* block_table, int max_pages,
+                                          const int* req_slots, const int* kv_len, void* out, float* scratch,
+                                          int batch, int num_q, int num_kv, int head_dim, int page_size, int window,
+                                          float scale, int num_splits, long long num_pages, int* status, void* stream,
+                                          int keep_first) {
+  if (keep_first < 0) return ULLM_ERR_BAD_SIZE;
+  DecFuse fu = {};
+  fu.keep_first = window > 0 ? keep_first : 0;
+  return decode_attention_impl(q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, scratch,
+                               batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits, num_pages, status,
+                               stream, fu);
+}
+
 // The same with q, the new key and the new value taken as the projection left them: the kernel applies the
 // per-head RMSNorm (weights may be null) and the rotation itself and writes key and value to their cache slot
 // (`slot_mapping` null: nothing is written).  qkv rows: [q heads | k heads | v heads], one row per request.
@@ -650,6 +670,7 @@ extern "C" int ullm_decode_attention_fused(const void* qkv, long long q_row_stri
   fu.num_slots = num_pages * page_size;
   fu.max_positions = max_positions;
   fu.eps = eps;
+  fu.keep_first = 0;
   return decode_attention_impl(qkv, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out,
                                scratch, batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits, num_pages,
                                status, stream, fu);

@@ -77,7 +77,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_slots,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len, int num_requests, int num_q,
-                         int num_kv, int page_size, int window, float scale_log2, long long num_pages, int* status) {
+                         int num_kv, int page_size, int window, float scale_log2, long long num_pages, int* status,
+                         int keep_first) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -126,7 +127,11 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
     return;
   }
   const int key0 = window > 0 ? max(0, p0 - window + 1) : 0;
-  const int tiles = (p1 - key0 + PRE_N) / PRE_N;
+  // With kept first positions the block's key tiles are: those of positions 0 .. kept - 1 (what the window of
+  // the block's first token has left behind of them), then those from key0 on.
+  const int kept = min(keep_first, key0);
+  const int sink_tiles = (kept + PRE_N - 1) / PRE_N;
+  const int tiles = sink_tiles + (p1 - key0 + PRE_N) / PRE_N;
   const int* bt = block_table + (long long)req_slots[r] * max_pages;
   const long long kv_row = (long long)num_kv * D;
 
@@ -146,9 +151,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
     unsigned char* vbuf = kbuf + S::TILE_BYTES;
     long long* slots = slot_s + st * PRE_N;
     if (tid < PRE_N) {
-      const int key = key0 + tile * PRE_N + tid;
+      const int key = tile < sink_tiles ? tile * PRE_N + tid : key0 + (tile - sink_tiles) * PRE_N + tid;
       long long s = -1;
-      if (key <= p1) {
+      if (tile < sink_tiles ? key < kept : key <= p1) {
         const int page = bt[key / page_size];
         if (page < 0 || page >= num_pages) ullm_report(status, ULLM_STATUS_PAGE, r, page);
         else s = (long long)page * page_size + key % page_size;
@@ -205,8 +210,10 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
     pre_commit();
     pre_wait<1>();
     __syncthreads();
-    const int kb = key0 + it * PRE_N;
-    if (warp_live && kb <= wp_max && kb + PRE_N - 1 >= wp_lo) {
+    const bool sink = it < sink_tiles;
+    const int kb = sink ? it * PRE_N : key0 + (it - sink_tiles) * PRE_N;
+    const int k_end = sink ? kept : 0x7fffffff;  // keys of a kept tile count below `kept` only
+    if (warp_live && (sink || (kb <= wp_max && (kb + PRE_N - 1 >= wp_lo || kb < keep_first)))) {
       const unsigned char* kbuf = kv_s + (it & 1) * 2 * S::TILE_BYTES;
       const unsigned char* vbuf = kbuf + S::TILE_BYTES;
       float sc[2][NT_S][4];
@@ -237,7 +244,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
       // Scores stay raw (unscaled) until the exponential: p = 2^(s * scale_log2 - m), one fused
       // multiply-add and one ex2 per element; m is kept in scaled units.  Only tiles that touch the
       // diagonal, a window's edge or padding rows run the mask.
-      const bool need_mask = !warp_full || kb + PRE_N - 1 > wp_min || (window > 0 && kb < wp_max - window + 1);
+      const bool need_mask = sink || !warp_full || kb + PRE_N - 1 > wp_min || (window > 0 && kb < wp_max - window + 1);
       float alpha[2][2];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
@@ -247,7 +254,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int key = kb + t * 8 + (lane & 3) * 2 + (e & 1);
-              if (!(key <= pos[mt][e >> 1] && key >= lo[mt][e >> 1])) sc[mt][t][e] = -INFINITY;
+              if (!(key <= pos[mt][e >> 1] && key < k_end && (key >= lo[mt][e >> 1] || key < keep_first)))
+                sc[mt][t][e] = -INFINITY;
             }
           }
         }
@@ -338,7 +346,8 @@ template <int D>
 static int launch_prefill(int which, const void* q, long long q_row_stride, void* out, const void* k_cache,
                           const void* v_cache, const int* block_table, int max_pages, const int* req_slots,
                           const int* cu_q, const int* kv_len, int tokens, int num_requests, int num_q, int num_kv,
-                          int page_size, int window, float scale, long long num_pages, int* status, cudaStream_t st) {
+                          int page_size, int window, float scale, long long num_pages, int* status, cudaStream_t st,
+                          int keep_first) {
   using S = PrefillSmem<D>;
   if (!g_prefill_attr_set[which]) {
     if (cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
@@ -354,7 +363,7 @@ static int launch_prefill(int which, const void* q, long long q_row_stride, void
   return ullm_launch_kernel(prefill_attention_kernel<D>, grid, dim3(PRE_WARPS * 32), (size_t)S::BYTES, st,
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, block_table, max_pages, req_slots, cu_q, kv_len, num_requests, num_q, num_kv,
-      page_size, window, scale * 1.4426950408889634f, num_pages, status);
+      page_size, window, scale * 1.4426950408889634f, num_pages, status, window > 0 ? keep_first : 0);
   return ullm_launch_status();
 }
 
@@ -364,19 +373,30 @@ extern "C" int ullm_prefill_attention_supported(int head_dim, int num_q, int num
   return (head_dim == 64 || head_dim == 128) && (num_q / num_kv) <= 32;
 }
 
-extern "C" int ullm_prefill_attention(const void* q, long long q_row_stride, void* out, const void* k_cache,
+// `keep_first`: with a window, the positions below it stay visible.
+extern "C" int ullm_prefill_attention_kept(const void* q, long long q_row_stride, void* out, const void* k_cache,
                                       const void* v_cache, const int* block_table, int max_pages, const int* req_slots,
                                       const int* cu_q, const int* kv_len, int tokens, int num_requests, int num_q,
                                       int num_kv, int head_dim, int page_size, int window, float scale,
-                                      long long num_pages, int* status, void* stream) {
+                                      long long num_pages, int* status, void* stream, int keep_first) {
   cudaStream_t st = (cudaStream_t)stream;
-  if (tokens < 0 || num_requests <= 0 || num_q <= 0 || num_kv <= 0 || page_size <= 0 || max_pages <= 0 || window < 0)
+  if (tokens < 0 || num_requests <= 0 || num_q <= 0 || num_kv <= 0 || page_size <= 0 || max_pages <= 0 || window < 0 || keep_first < 0)
     return ULLM_ERR_BAD_SIZE;
   if (!ullm_prefill_attention_supported(head_dim, num_q, num_kv)) return ULLM_ERR_UNSUPPORTED;
   if (tokens == 0) return ULLM_OK;
   if (head_dim == 64)
     return launch_prefill<64>(0, q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
-                              tokens, num_requests, num_q, num_kv, page_size, window, scale, num_pages, status, st);
+                              tokens, num_requests, num_q, num_kv, page_size, window, scale, num_pages, status, st, keep_first);
   return launch_prefill<128>(1, q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
-                             tokens, num_requests, num_q, num_kv, page_size, window, scale, num_pages, status, st);
+                             tokens, num_requests, num_q, num_kv, page_size, window, scale, num_pages, status, st, keep_first);
+}
+
+extern "C" int ullm_prefill_attention(const void* q, long long q_row_stride, void* out, const void* k_cache,
+                                      const void* v_cache, const int* block_table, int max_pages, const int* req_slots,
+                                      const int* cu_q, const int* kv_len, int tokens, int num_requests, int num_q,
+                                      int num_kv, int head_dim, int page_size, int window, float scale,
+                                      long long num_pages, int* status, void* stream) {
+  return ullm_prefill_attention_kept(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                     kv_len, tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale,
+                                     num_pages, status, stream, 0);
 }

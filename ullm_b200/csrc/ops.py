@@ -217,6 +217,8 @@ class Kernels:
             "ullm_decode_attention_fused": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, F, P, P, I,
                                             P, P, P, P],
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
+            "ullm_prefill_attention_kept": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P, I],
+            "ullm_decode_attention_kept": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, I],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_pair": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
@@ -965,10 +967,13 @@ class Kernels:
                                             qkv.stride(0)) == "split")
 
     def _decode_rows(self, qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
-                     page_size, window, scale, num_pages, ragged, ctx, fuse=None) -> None:
-        """Decode attention of T one-token rows (row i belongs to request row i): streams the pages once."""
+                     page_size, window, scale, num_pages, ragged, ctx, fuse=None, keep_first: int = 0) -> None:
+        """Decode attention of T one-token rows (row i belongs to request row i): streams the pages once.
+        `keep_first` > 0 (with a window): the per-request split kernel, the one that takes kept first positions."""
         T = out.shape[0]
         choice = self._decode_choice(T, ragged, num_q, num_kv, head_dim, page_size, qkv.stride(0))
+        if keep_first > 0:
+            choice = "split"
         if fuse is not None and choice != "split":
             raise KernelError("decode attention: q and k were left unprepared for a kernel that does not prepare them")
         tc = choice == "tcgen05"
@@ -1029,6 +1034,12 @@ class Kernels:
                 _ptr(fuse["cos"]), _ptr(fuse["sin"]), fuse["cos"].shape[0], _ptr(fuse["positions"]),
                 _ptr(fuse["slot_mapping"]), _ptr(self.status), _stream()),
                 f"decode_attention_fused (head_dim {head_dim})")
+        elif keep_first > 0:
+            self._check(self.lib.ullm_decode_attention_kept(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
+                int(window), float(scale), splits, num_pages, _ptr(self.status), _stream(), int(keep_first)),
+                f"decode_attention (head_dim {head_dim}, first {keep_first} kept)")
         else:
             self._check(self.lib.ullm_decode_attention(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
@@ -1063,9 +1074,29 @@ class Kernels:
             raise KernelError(f"paged_attention: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} != "
                               f"[*, {page_size}, {num_kv}, {head_dim} / {v_dim}]")
         num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
+        if keep_first > 0 and not window:
+            keep_first = 0
+        kept_tc = (keep_first > 0 and v_dim == head_dim and ctx is not None and qkv.dtype == torch.bfloat16
+                   and fuse is None and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)
+                   and self.lib.ullm_prefill_attention_supported(head_dim, num_q, num_kv))
+        if kept_tc:
+            # kept first positions on the tensor cores (head size 64 or 128): decode steps on the per-request split
+            # kernel, steps with prompt portions on the mma.sync prompt kernel; both number a row's visible keys
+            # "kept ones, then the window" and leave everything else as it is
+            if ctx.decode_only and T == ctx.num_requests:
+                self._decode_rows(qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
+                                  page_size, window, scale, num_pages, False, ctx, None, keep_first)
+                return
+            self._check(self.lib.ullm_prefill_attention_kept(
+                _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, ctx.num_requests, num_q, num_kv,
+                head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream(),
+                int(keep_first)), f"prefill_attention (head_dim {head_dim}, first {keep_first} kept)")
+            self.attention_path = "prefill"
+            return
         if v_dim != head_dim or keep_first > 0:
-            # values of a head size of their own, or first positions that stay visible behind the window: the
-            # general kernel (the tensor-core kernels take neither)
+            # values of a head size of their own, or kept first positions at other head sizes or in 32-bit: the
+            # general kernel
             if fuse is not None:
                 raise KernelError("paged_attention: q and k were left unprepared, but the general kernel takes this step")
             self.attention_path = "generic"
