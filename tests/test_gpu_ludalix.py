@@ -157,6 +157,37 @@ def test_feed_forwards_alone(tmp_path, dtype):
                 close(got, ref, dtype, f"{tag} layer {l} {mlp['kind']}")
 
 
+@pytest.mark.needs_cuda
+def test_routed_experts_on_tensor_cores_agree_with_the_plain_grouped_product(tmp_path):
+    """Sizes that allow 16-byte pieces take the tensor-core grouped product in bfloat16; the same step with that
+    kernel switched off must give the same rows up to the order of additions, and both follow the plain model.
+    200 tokens over 5 experts: tiles of 64 places with ragged ends, and an expert's columns that end inside a tile."""
+    from ullm_b200.csrc import kernels
+    from ullm_b200.engine.batch import Workspace
+
+    cfg = config(72, 64, [("mlstm", mlstm(1, 8, 8, 5.0), moe(5, 2, 88))])
+    w = {n: t.to(torch.bfloat16) for n, t in pl.random_weights(cfg, seed=8).items()}
+    r = make_runner(tmp_path, cfg, w, 8, "bfloat16")
+
+    class Ctx:
+        workspace = Workspace(r.device, max_tokens=256, max_requests=4)
+
+    x = rand((200, 72), 3, "bfloat16", 1.5)
+    ff = r.model.blocks[0].feed_forward
+    fast = ff.forward(x.clone(), Ctx()).float().cpu().clone()
+    kernels().moe_force_plain(True)
+    try:
+        slow = ff.forward(x.clone(), Ctx()).float().cpu().clone()
+    finally:
+        kernels().moe_force_plain(False)
+    assert (fast - slow).abs().max() <= 2e-2 * slow.abs().max()
+    ref = pl.feed_forward(x.double().cpu(), {n: t.double() for n, t in w.items()}, "l0.mlp.", cfg["layers"][0]["mlp"]).float()
+    s = torch.sigmoid(x.double().cpu() @ w["l0.mlp.router"].double().T).sort(-1, descending=True).values
+    clear = (s[:, 1] - s[:, 2]) > 0.005
+    assert clear.sum() > 150
+    assert_close(fast[clear], ref[clear], "bfloat16", "routed experts on tensor cores")
+
+
 def test_router_weight_multiplies_the_experts_input_not_its_output():
     """The oracle's own reading: with one expert per token the two readings differ, and the engine follows the
     first (checked through the whole model elsewhere; here the plain functions are pinned)."""

@@ -13,8 +13,9 @@
 // The recurrence is run token by token, so a request's result does not depend on how its tokens were cut into
 // steps.  The parallelism is over requests, heads and the columns of S: a block owns (request, head, a tile of
 // columns); a column's d rows are spread over RS neighbouring lanes (row r belongs to lane r mod RS), which meet
-// in shuffles for the two dot products.  q, k and the tile's v of a chunk of tokens are staged in shared memory,
-// the gates of the chunk are evaluated once per block.
+// in shuffles for the two dot products.  q, k and the tile's v of a chunk of tokens are staged in shared memory
+// and the chunk's gates evaluated by a second set of threads of the block while the first set runs the chunk
+// before (two buffers).
 //
 // State row layout (floats): S^T as [heads][dv][d], then n [heads][d], then m [heads].
 //
@@ -28,20 +29,24 @@
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
 template <typename T>
-__global__ void __launch_bounds__(MLSTM_THREADS)
+__global__ void __launch_bounds__(2 * MLSTM_THREADS)
 mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off, int k_off, int v_off,
                         const float* __restrict__ gates, const float* __restrict__ bias_i,
                         const float* __restrict__ bias_f, float* __restrict__ state, long long state_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ req_slots,
                         const int* __restrict__ token_req, float* __restrict__ out, int heads, int dim, int vdim,
                         int rs, int chunk, float q_scale, float cap, int num_slots, int* status) {
+  // Threads 0 .. 127 run the recurrence; threads 128 .. 255 stage the next chunk of tokens (q, k, the tile's v,
+  // the evaluated gates) in the other half of shared memory meanwhile, so the recurrence never waits for memory.
   extern __shared__ float sm[];
   pdl_launch_dependents();
   pdl_wait();
   const int req = blockIdx.z, head = blockIdx.y;
   const int cols_per_block = MLSTM_THREADS / rs;
-  const int lane_row = threadIdx.x % rs;          // which rows: lane_row, lane_row + rs, ...
-  const int col_in_block = threadIdx.x / rs;
+  const bool loader = threadIdx.x >= MLSTM_THREADS;
+  const int tid = threadIdx.x & (MLSTM_THREADS - 1);
+  const int lane_row = tid % rs;          // which rows: lane_row, lane_row + rs, ...
+  const int col_in_block = tid / rs;
   const int col = blockIdx.x * cols_per_block + col_in_block;
   const bool col_ok = col < vdim;
   const int t0 = cu_q[req], t1 = cu_q[req + 1];
@@ -53,15 +58,66 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
     return;
   }
   if (padding) {
-    if (lane_row == 0 && col_ok)
+    if (!loader && lane_row == 0 && col_ok)
       for (int t = t0; t < t1; ++t) out[((long long)t * heads + head) * vdim + col] = 0.f;
     return;
   }
-  float* sq = sm;                        // [chunk][dim]
-  float* sk = sq + chunk * dim;          // [chunk][dim]
-  float* sv = sk + chunk * dim;          // [chunk][cols_per_block]
-  float* sgi = sv + chunk * cols_per_block;  // [chunk]
-  float* sgf = sgi + chunk;              // [chunk]
+  const int buf_floats = 2 * chunk * dim + chunk * cols_per_block + 2 * chunk;
+  const float bi = bias_i != nullptr ? bias_i[head] : 0.f, bf = bias_f != nullptr ? bias_f[head] : 0.f;
+
+  // stages tokens c0 .. c0 + cn - 1 into buffer `which` (loader threads only)
+  auto fill = [&](int which, int c0, int cn) {
+    float* sq = sm + which * buf_floats;   // [chunk][dim]
+    float* sk = sq + chunk * dim;          // [chunk][dim]
+    float* sv = sk + chunk * dim;          // [chunk][cols_per_block]
+    float* sgi = sv + chunk * cols_per_block;
+    float* sgf = sgi + chunk;
+    const int n_qk = cn * dim;
+    for (int e0 = tid; e0 < n_qk; e0 += MLSTM_THREADS * 8) {
+      float tq[8], tk[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = e0 + j * MLSTM_THREADS;
+        if (e < n_qk) {
+          const int t = e / dim, r = e - t * dim;
+          const T* row = qkv + (long long)(c0 + t) * row_stride + head * dim + r;
+          tq[j] = to_f32(row[q_off]);
+          tk[j] = to_f32(row[k_off]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int e = e0 + j * MLSTM_THREADS;
+        if (e < n_qk) {
+          sq[e] = tq[j] * q_scale;
+          sk[e] = tk[j];
+        }
+      }
+    }
+    const int n_v = cn * cols_per_block;
+    for (int e0 = tid; e0 < n_v; e0 += MLSTM_THREADS * 4) {
+      float tv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j * MLSTM_THREADS;
+        tv[j] = 0.f;
+        if (e < n_v) {
+          const int t = e / cols_per_block, cj = blockIdx.x * cols_per_block + (e - t * cols_per_block);
+          if (cj < vdim) tv[j] = to_f32(qkv[(long long)(c0 + t) * row_stride + v_off + head * vdim + cj]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j * MLSTM_THREADS;
+        if (e < n_v) sv[e] = tv[j];
+      }
+    }
+    if (tid < cn) {
+      const float* g = gates + (long long)(c0 + tid) * 2 * heads;
+      sgi[tid] = cap * tanhf((g[head] + bi) / cap);
+      sgf[tid] = log_sigmoid(cap * tanhf((g[heads + head] + bf) / cap));
+    }
+  };
 
   float* st_row = state + (long long)slot * state_stride;
   float* st_S = st_row + ((long long)head * vdim + (col_ok ? col : 0)) * dim;
@@ -69,66 +125,74 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
   float* st_m = st_row + (long long)heads * vdim * dim + (long long)heads * dim + head;
 
   float S[MLSTM_RPT], n[MLSTM_RPT];
+  float m = 0.f;
+  if (!loader) {
 #pragma unroll
-  for (int i = 0; i < MLSTM_RPT; ++i) {
-    const int r = lane_row + rs * i;
-    const bool on = r < dim;
-    S[i] = (on && col_ok) ? st_S[r] : 0.f;
-    n[i] = on ? st_n[r] : 0.f;
+    for (int i = 0; i < MLSTM_RPT; ++i) {
+      const int r = lane_row + rs * i;
+      const bool on = r < dim;
+      S[i] = (on && col_ok) ? st_S[r] : 0.f;
+      n[i] = on ? st_n[r] : 0.f;
+    }
+    m = *st_m;
+  } else {
+    fill(0, t0, min(chunk, t1 - t0));
   }
-  float m = *st_m;
-  const float bi = bias_i != nullptr ? bias_i[head] : 0.f, bf = bias_f != nullptr ? bias_f[head] : 0.f;
+  __syncthreads();
 
-  for (int c0 = t0; c0 < t1; c0 += chunk) {
+  int which = 0;
+  for (int c0 = t0; c0 < t1; c0 += chunk, which ^= 1) {
     const int cn = min(chunk, t1 - c0);
-    __syncthreads();  // the chunk before has been used up
-    for (int e = threadIdx.x; e < cn * dim; e += MLSTM_THREADS) {
-      const int t = e / dim, r = e - t * dim;
-      const T* row = qkv + (long long)(c0 + t) * row_stride;
-      sq[e] = to_f32(row[q_off + head * dim + r]) * q_scale;
-      sk[e] = to_f32(row[k_off + head * dim + r]);
-    }
-    for (int e = threadIdx.x; e < cn * cols_per_block; e += MLSTM_THREADS) {
-      const int t = e / cols_per_block, j = e - t * cols_per_block;
-      const int cj = blockIdx.x * cols_per_block + j;
-      sv[e] = cj < vdim ? to_f32(qkv[(long long)(c0 + t) * row_stride + v_off + head * vdim + cj]) : 0.f;
-    }
-    if (threadIdx.x < cn) {
-      const float* g = gates + (long long)(c0 + threadIdx.x) * 2 * heads;
-      sgi[threadIdx.x] = cap * tanhf((g[head] + bi) / cap);
-      sgf[threadIdx.x] = log_sigmoid(cap * tanhf((g[heads + head] + bf) / cap));
-    }
-    __syncthreads();
-    for (int t = 0; t < cn; ++t) {
-      const float fi = sgf[t], ii = sgi[t];
-      const float m_new = fmaxf(fi + m, ii);
-      const float keep = expf(fi + m - m_new), take = expf(ii - m_new);
-      m = m_new;
-      const float tv = take * sv[t * cols_per_block + col_in_block];
-      const float* kq = sk + t * dim;
-      const float* qq = sq + t * dim;
-      float dot = 0.f, ndot = 0.f;
+    if (loader) {
+      if (c0 + chunk < t1) fill(which ^ 1, c0 + chunk, min(chunk, t1 - c0 - chunk));
+    } else {
+      const float* sq = sm + which * buf_floats;
+      const float* sk = sq + chunk * dim;
+      const float* sv = sk + chunk * dim;
+      const float* sgi = sv + chunk * cols_per_block;
+      const float* sgf = sgi + chunk;
+      for (int t = 0; t < cn; ++t) {
+        const float fi = sgf[t], ii = sgi[t];
+        const float m_new = fmaxf(fi + m, ii);
+        const float keep = expf(fi + m - m_new), take = expf(ii - m_new);
+        m = m_new;
+        const float tv = take * sv[t * cols_per_block + col_in_block];
+        const float* kq = sk + t * dim;
+        const float* qq = sq + t * dim;
+        float dot = 0.f, ndot = 0.f, dot2 = 0.f, ndot2 = 0.f;
 #pragma unroll
-      for (int i = 0; i < MLSTM_RPT; ++i) {
-        const int r = lane_row + rs * i;
-        if (r < dim) {
-          const float kr = kq[r], qr = qq[r];
-          S[i] = fmaf(keep, S[i], kr * tv);
-          n[i] = fmaf(keep, n[i], take * kr);
-          dot = fmaf(S[i], qr, dot);
-          ndot = fmaf(n[i], qr, ndot);
+        for (int i = 0; i < MLSTM_RPT; i += 2) {
+          const int r = lane_row + rs * i, r2 = r + rs;
+          if (r < dim) {
+            const float kr = kq[r], qr = qq[r];
+            S[i] = fmaf(keep, S[i], kr * tv);
+            n[i] = fmaf(keep, n[i], take * kr);
+            dot = fmaf(S[i], qr, dot);
+            ndot = fmaf(n[i], qr, ndot);
+          }
+          if (r2 < dim) {
+            const float kr = kq[r2], qr = qq[r2];
+            S[i + 1] = fmaf(keep, S[i + 1], kr * tv);
+            n[i + 1] = fmaf(keep, n[i + 1], take * kr);
+            dot2 = fmaf(S[i + 1], qr, dot2);
+            ndot2 = fmaf(n[i + 1], qr, ndot2);
+          }
+        }
+        dot += dot2;
+        ndot += ndot2;
+        for (int o = rs >> 1; o > 0; o >>= 1) {
+          dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
+        }
+        if (lane_row == 0 && col_ok) {
+          const float den = fmaxf(fabsf(ndot), expf(-m)) + 1e-6f;
+          out[((long long)(c0 + t) * heads + head) * vdim + col] = dot / den;
         }
       }
-      for (int o = rs >> 1; o > 0; o >>= 1) {
-        dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
-      }
-      if (lane_row == 0 && col_ok) {
-        const float den = fmaxf(fabsf(ndot), expf(-m)) + 1e-6f;
-        out[((long long)(c0 + t) * heads + head) * vdim + col] = dot / den;
-      }
     }
+    __syncthreads();  // the next chunk is staged, this one used up
   }
+  if (loader) return;
 #pragma unroll
   for (int i = 0; i < MLSTM_RPT; ++i) {
     const int r = lane_row + rs * i;
@@ -137,7 +201,7 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
       if (blockIdx.x == 0 && col_in_block == 0) st_n[r] = n[i];
     }
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) *st_m = m;
+  if (blockIdx.x == 0 && tid == 0) *st_m = m;
 }
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * w[h, :] * sigmoid(g[t, h, :]); one warp per (token, head).
@@ -187,10 +251,12 @@ static int mlstm_launch(const void* qkv, long long row_stride, int q_off, int k_
                         cudaStream_t st) {
   const int rs = mlstm_rs(dim);
   const int cols = MLSTM_THREADS / rs;
-  const int chunk = dim <= 256 ? 16 : 8;
-  const size_t smem = (size_t)(2 * chunk * dim + chunk * cols + 2 * chunk) * sizeof(float);
+  // tokens per staged chunk: two buffers of (2 dim + cols + 2) floats a token stay below 48 KB
+  int chunk = 16;
+  while (chunk > 1 && (size_t)2 * chunk * (2 * dim + cols + 2) * sizeof(float) > 46 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * (2 * chunk * dim + chunk * cols + 2 * chunk) * sizeof(float);
   const dim3 grid((vdim + cols - 1) / cols, heads, requests);
-  return ullm_launch_kernel(mlstm_recurrence_kernel<T>, grid, dim3(MLSTM_THREADS), smem, st, (const T*)qkv,
+  return ullm_launch_kernel(mlstm_recurrence_kernel<T>, grid, dim3(2 * MLSTM_THREADS), smem, st, (const T*)qkv,
                             row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state, state_stride, cu_q,
                             req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale, cap, num_slots, status);
 }

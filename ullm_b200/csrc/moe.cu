@@ -203,6 +203,164 @@ moe_grouped_linear_kernel(const T* __restrict__ x, long long x_stride, const T* 
   }
 }
 
+// ---------------------------------------------------------------------------
+// The grouped product on the tensor cores (bfloat16, mma.sync m16n8k16, 32-bit accumulation): a block owns 64
+// places of one expert x 64 output columns (gate and up columns both when GATED); x rows (gathered by place) and
+// weight rows go through a two-stage cp.async ring of 64-element k slices in 128-byte rows with the chunk index
+// XORed by the row (conflict-free ldmatrix).  Needs k_dim, the row stride of x and n_out to allow 16-byte pieces
+// and paired stores; the launcher falls back to the kernel above otherwise.
+// ---------------------------------------------------------------------------
+#define MMA_BM 64
+#define MMA_BN 64
+#define MMA_BK 64
+#define MMA_THREADS 128
+
+__device__ __forceinline__ void moe_cp_async_16(void* smem, const void* gmem, bool pred) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = pred ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void moe_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void moe_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void moe_ldsm4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(s));
+}
+__device__ __forceinline__ void moe_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(MMA_THREADS)
+moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
+                       const __nv_bfloat16* __restrict__ weights, long long expert_stride,
+                       const int* __restrict__ offsets, const int* __restrict__ sorted,
+                       const float* __restrict__ pair_weight, __nv_bfloat16* __restrict__ out, int experts, int top,
+                       int rows_from_pairs, int n_out, int k_dim, int act) {
+  constexpr int NB = GATED ? 2 : 1;
+  constexpr int TILE = MMA_BM * MMA_BK * 2;  // bytes of one 64 x 64 tile
+  extern __shared__ __align__(128) unsigned char moe_smem[];
+  __shared__ int s_row[MMA_BM];
+  __shared__ float s_scale[MMA_BM];
+  pdl_launch_dependents();
+  pdl_wait();
+  int e = 0, tile = blockIdx.y, lo = 0, hi = 0;
+  for (; e < experts; ++e) {
+    lo = offsets[e];
+    hi = offsets[e + 1];
+    const int tiles = (hi - lo + MMA_BM - 1) / MMA_BM;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  if (e >= experts) return;
+  const int p0 = lo + tile * MMA_BM;
+  const int rows = min(MMA_BM, hi - p0);
+  const int n0 = blockIdx.x * MMA_BN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < MMA_BM) {
+    int src = 0;
+    float sc = 0.f;
+    if (tid < rows) {
+      const int pair = sorted[p0 + tid];
+      src = rows_from_pairs ? pair / top : p0 + tid;
+      sc = pair_weight != nullptr ? pair_weight[pair] : 1.f;
+    }
+    s_row[tid] = src;
+    s_scale[tid] = sc;
+  }
+  __syncthreads();
+  const __nv_bfloat16* W = weights + (long long)e * expert_stride;
+  unsigned char* a_s = moe_smem;                 // [2][TILE]
+  unsigned char* b_s = moe_smem + 2 * TILE;      // [2][NB][TILE]
+  const int ksteps = (k_dim + MMA_BK - 1) / MMA_BK;
+
+  auto issue = [&](int kt) {
+    const int st = kt & 1;
+    const int k0 = kt * MMA_BK;
+#pragma unroll
+    for (int i = 0; i < MMA_BM * 8 / MMA_THREADS; ++i) {
+      const int c = i * MMA_THREADS + tid;
+      const int row = c >> 3, ch = c & 7;
+      const bool k_ok = k0 + ch * 8 < k_dim;
+      const int sw = row * 128 + ((ch ^ (row & 7)) * 16);
+      const bool a_ok = k_ok && row < rows;
+      moe_cp_async_16(a_s + st * TILE + sw, x + (a_ok ? (long long)s_row[row] * x_stride + k0 + ch * 8 : 0), a_ok);
+      const bool b_ok = k_ok && n0 + row < n_out;
+#pragma unroll
+      for (int g = 0; g < NB; ++g)
+        moe_cp_async_16(b_s + (st * NB + g) * TILE + sw,
+                        W + (b_ok ? ((long long)(g * n_out + n0 + row) * k_dim + k0 + ch * 8) : 0), b_ok);
+    }
+  };
+
+  float acc[NB][8][4];
+#pragma unroll
+  for (int g = 0; g < NB; ++g)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) acc[g][t][0] = acc[g][t][1] = acc[g][t][2] = acc[g][t][3] = 0.f;
+
+  issue(0);
+  moe_commit();
+  for (int kt = 0; kt < ksteps; ++kt) {
+    if (kt + 1 < ksteps) issue(kt + 1);
+    moe_commit();
+    moe_wait<1>();
+    __syncthreads();
+    const unsigned char* at = a_s + (kt & 1) * TILE;
+#pragma unroll
+    for (int kk = 0; kk < MMA_BK / 16; ++kk) {
+      unsigned a[4];
+      {
+        const int mat = lane >> 3, row = warp * 16 + (mat & 1) * 8 + (lane & 7), ch = 2 * kk + (mat >> 1);
+        moe_ldsm4(a[0], a[1], a[2], a[3], at + row * 128 + ((ch ^ (row & 7)) * 16));
+      }
+#pragma unroll
+      for (int g = 0; g < NB; ++g) {
+        const unsigned char* bt = b_s + ((kt & 1) * NB + g) * TILE;
+#pragma unroll
+        for (int t = 0; t < 8; t += 2) {
+          const int mat = lane >> 3, row = t * 8 + (mat >> 1) * 8 + (lane & 7), ch = 2 * kk + (mat & 1);
+          unsigned b0, b1, b2, b3;
+          moe_ldsm4(b0, b1, b2, b3, bt + row * 128 + ((ch ^ (row & 7)) * 16));
+          moe_mma(acc[g][t], a, b0, b1);
+          moe_mma(acc[g][t + 1], a, b2, b3);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + (lane >> 2) + h * 8;
+    if (r >= rows) continue;
+    const float sc = s_scale[r];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      const int c = n0 + t * 8 + (lane & 3) * 2;
+      if (c >= n_out) continue;  // (n_out is even: a pair is inside or outside)
+      float v[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        if (GATED) {
+          const float gt = acc[0][t][2 * h + j] * sc, up = acc[NB - 1][t][2 * h + j] * sc;
+          v[j] = (act == 0 ? act_silu(gt) : act_gelu_tanh(gt)) * up;
+        } else {
+          v[j] = acc[0][t][2 * h + j] * sc;
+        }
+      }
+      *reinterpret_cast<__nv_bfloat162*>(out + (long long)(p0 + r) * n_out + c) = __floats2bfloat162_rn(v[0], v[1]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __restrict__ place,
                                    const float* __restrict__ pair_weight, T* __restrict__ y, int top, int cols) {
@@ -219,6 +377,10 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
     y[t * cols + c] = from_f32<T>(s);
   }
 }
+
+static int g_moe_force_plain = 0;
+// 1: the grouped product never takes the tensor-core kernel (tests compare the two)
+extern "C" void ullm_moe_force_plain(int on) { g_moe_force_plain = on ? 1 : 0; }
 
 extern "C" int ullm_moe_route(const float* logits, int* choice, float* weight, int tokens, int experts, int top,
                               int softmax_scores, int renormalize, void* stream) {
@@ -267,9 +429,35 @@ extern "C" int ullm_moe_grouped_linear(int dtype, const void* x, long long x_str
   if (dtype == ULLM_DTYPE_F32)
     return grouped_launch<float>(x, x_stride, weights, expert_stride, offsets, sorted, pair_weight, out, pairs,
                                  experts, top, rows_from_pairs, n_out, k_dim, gated, act, st);
-  if (dtype == ULLM_DTYPE_BF16)
+  if (dtype == ULLM_DTYPE_BF16) {
+    const bool tensor_cores = !g_moe_force_plain && k_dim % 8 == 0 && x_stride % 8 == 0 && n_out % 2 == 0 &&
+                              (uintptr_t)x % 16 == 0 && (uintptr_t)weights % 16 == 0 && (uintptr_t)out % 4 == 0 &&
+                              expert_stride % 8 == 0;
+    if (tensor_cores) {
+      const int row_tiles = (pairs + MMA_BM - 1) / MMA_BM + experts;
+      if (row_tiles > 65535) return ULLM_ERR_BAD_SIZE;
+      const dim3 grid((n_out + MMA_BN - 1) / MMA_BN, row_tiles), block(MMA_THREADS);
+      const size_t smem = (size_t)2 * (1 + (gated ? 2 : 1)) * MMA_BM * MMA_BK * 2;
+      static int attr_set = 0;
+      if (!attr_set) {  // (with the static arrays the gated form is just above the size a kernel gets unasked)
+        if (cudaFuncSetAttribute(moe_grouped_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) !=
+                cudaSuccess ||
+            cudaFuncSetAttribute(moe_grouped_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) !=
+                cudaSuccess)
+          return ULLM_ERR_LAUNCH;
+        attr_set = 1;
+      }
+      if (gated)
+        return ullm_launch_kernel(moe_grouped_mma_kernel<true>, grid, block, smem, st, (const __nv_bfloat16*)x, x_stride,
+                                  (const __nv_bfloat16*)weights, expert_stride, offsets, sorted, pair_weight,
+                                  (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act);
+      return ullm_launch_kernel(moe_grouped_mma_kernel<false>, grid, block, smem, st, (const __nv_bfloat16*)x, x_stride,
+                                (const __nv_bfloat16*)weights, expert_stride, offsets, sorted, pair_weight,
+                                (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act);
+    }
     return grouped_launch<__nv_bfloat16>(x, x_stride, weights, expert_stride, offsets, sorted, pair_weight, out,
                                          pairs, experts, top, rows_from_pairs, n_out, k_dim, gated, act, st);
+  }
   if (dtype == ULLM_DTYPE_F16)
     return grouped_launch<__half>(x, x_stride, weights, expert_stride, offsets, sorted, pair_weight, out, pairs,
                                   experts, top, rows_from_pairs, n_out, k_dim, gated, act, st);

@@ -249,6 +249,8 @@ class Kernels:
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = c_int
+        L.ullm_moe_force_plain.argtypes = [I]
+        L.ullm_moe_force_plain.restype = None
         L.ullm_mlstm_supported.argtypes = [I, I, I]
         L.ullm_mlstm_supported.restype = c_int
         L.ullm_mlstm_state_floats.argtypes = [I, I, I]
@@ -870,6 +872,10 @@ class Kernels:
             _DT[x.dtype], _ptr(x), x.stride(0), _ptr(weights), weights.stride(0), _ptr(offsets), _ptr(sorted_pairs),
             _ptr(pair_weight), _ptr(out), pairs, E, top, int(rows_from_pairs), n_out, K, int(gated), act, _stream()),
             f"moe_grouped_linear ({E} experts, {N} x {K})")
+
+    def moe_force_plain(self, on: bool) -> None:
+        """True: the grouped product never takes its tensor-core kernel (tests compare the two)."""
+        self.lib.ullm_moe_force_plain(1 if on else 0)
 
     @_timed("moe")
     def moe_combine(self, rows, place, pair_weight, y, top: int):
