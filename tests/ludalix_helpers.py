@@ -59,7 +59,13 @@ CFG_R = config(100, 130, [
     ("mlstm", mlstm(2, 12, 36, 12.0), moe(6, 2, 20)),
 ], mult=0.8, scale=4.0)
 
-CONFIGS = {"P": (CFG_P, 8), "Q": (CFG_Q, 4), "R": (CFG_R, 16)}  # config, page size
+# S: state heads of 128 and 256 rows (the recurrence kernel's forms without bounds checks), many value columns
+CFG_S = config(96, 77, [
+    ("mlstm", mlstm(2, 128, 24, 9.0), dense(64, 2.0)),
+    ("mlstm", mlstm(1, 256, 136, 9.0), None),
+], mult=0.7, scale=5.0)
+
+CONFIGS = {"P": (CFG_P, 8), "Q": (CFG_Q, 4), "R": (CFG_R, 16), "S": (CFG_S, 16)}  # config, page size
 
 
 def weights_for(tag: str, dtype: str, seed: int = 0, std_scale: float = 1.0):

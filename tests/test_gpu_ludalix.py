@@ -55,7 +55,7 @@ def test_embedding_with_added_sinusoid(tmp_path, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag,layer", [("P", 1), ("P", 3), ("Q", 0), ("R", 1)])
+@pytest.mark.parametrize("tag,layer", [("P", 1), ("P", 3), ("Q", 0), ("R", 1), ("S", 0), ("S", 1)])
 def test_mlstm_mixer_alone(tmp_path, dtype, tag, layer):
     """The mixer on random rows in three steps (13, 1 and 9 tokens) against the recurrence run whole."""
     from ullm_b200.engine import StepEntry
@@ -205,7 +205,7 @@ def test_router_weight_multiplies_the_experts_input_not_its_output():
 # whole prompts, token-by-token decoding, portions
 # ---------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["P", "Q", "R"])
+@pytest.mark.parametrize("tag", ["P", "Q", "R", "S"])
 def test_whole_decode_and_portions_agree_with_the_plain_model(tmp_path, dtype, tag):
     cfg, w, page = weights_for(tag, dtype)
     r = make_runner(tmp_path, cfg, w, page, dtype)

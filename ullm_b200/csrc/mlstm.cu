@@ -13,14 +13,17 @@
 // The recurrence is run token by token, so a request's result does not depend on how its tokens were cut into
 // steps.  The parallelism is over requests, heads and the columns of S: a block owns (request, head, a tile of
 // columns); a column's d rows are spread over RS neighbouring lanes (row r belongs to lane r mod RS), which meet
-// in shuffles for the two dot products.  q, k and the tile's v of a chunk of tokens are staged in shared memory
-// and the chunk's gates evaluated by a second set of threads of the block while the first set runs the chunk
-// before (two buffers).
+// in shuffles for the two dot products.  q, k and the tile's v of a chunk of tokens are staged in shared memory,
+// and the chunk's gates, running maximum and the three exponentials of every token evaluated, by a second set of
+// threads of the block while the first set runs the chunk before (two buffers): the first set is left with the
+// multiply-adds, the shuffles and one division per token.
 //
 // State row layout (floats): S^T as [heads][dv][d], then n [heads][d], then m [heads].
 //
 // A second kernel finishes the mixer's head: per (token, head) o / sqrt(mean(o^2) + eps) * w * sigmoid(g).
 #include "common.cuh"
+
+#include <type_traits>
 
 #define MLSTM_THREADS 128
 #define MLSTM_RPT 16       // rows of S a thread holds at most
@@ -28,14 +31,19 @@
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename T>
+// RPT: rows of S a thread holds at most (8 or MLSTM_RPT).  RS > 0: the lanes per column are known when the kernel
+// is compiled and dim == RS * RPT exactly, so the row loop has neither bounds checks nor address arithmetic left
+// (measured at dim 128: 2.5 times fewer instructions per token); RS == 0: any dim, lanes per column in `rs_arg`.
+template <typename T, int RPT, int RS>
 __global__ void __launch_bounds__(2 * MLSTM_THREADS)
 mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off, int k_off, int v_off,
                         const float* __restrict__ gates, const float* __restrict__ bias_i,
                         const float* __restrict__ bias_f, float* __restrict__ state, long long state_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ req_slots,
                         const int* __restrict__ token_req, float* __restrict__ out, int heads, int dim, int vdim,
-                        int rs, int chunk, float q_scale, float cap, int num_slots, int* status) {
+                        int rs_arg, int chunk, float q_scale, float cap, int num_slots, int* status) {
+  constexpr bool FULL = RS != 0;
+  const int rs = FULL ? RS : rs_arg;
   // Threads 0 .. 127 run the recurrence; threads 128 .. 255 stage the next chunk of tokens (q, k, the tile's v,
   // the evaluated gates) in the other half of shared memory meanwhile, so the recurrence never waits for memory.
   extern __shared__ float sm[];
@@ -62,17 +70,64 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
       for (int t = t0; t < t1; ++t) out[((long long)t * heads + head) * vdim + col] = 0.f;
     return;
   }
-  const int buf_floats = 2 * chunk * dim + chunk * cols_per_block + 2 * chunk;
+  const int buf_floats = (2 * chunk * dim + chunk * cols_per_block + 3 * chunk + 1 + 3) & ~3;  // (16-byte steps)
+  const bool vec8 = std::is_same<T, __nv_bfloat16>::value && (dim & 7) == 0 && (q_off & 7) == 0 && (k_off & 7) == 0 && (row_stride & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(qkv) & 15) == 0;
   const float bi = bias_i != nullptr ? bias_i[head] : 0.f, bf = bias_f != nullptr ? bias_f[head] : 0.f;
+
+  float* st_row = state + (long long)slot * state_stride;
+  float* st_S = st_row + ((long long)head * vdim + (col_ok ? col : 0)) * dim;
+  float* st_n = st_row + (long long)heads * vdim * dim + (long long)head * dim;
+  float* st_m = st_row + (long long)heads * vdim * dim + (long long)heads * dim + head;
+
+  float m_run = *st_m;  // the running maximum as the stagers carry it, one chunk ahead of the recurrence
 
   // stages tokens c0 .. c0 + cn - 1 into buffer `which` (loader threads only)
   auto fill = [&](int which, int c0, int cn) {
     float* sq = sm + which * buf_floats;   // [chunk][dim]
     float* sk = sq + chunk * dim;          // [chunk][dim]
     float* sv = sk + chunk * dim;          // [chunk][cols_per_block]
-    float* sgi = sv + chunk * cols_per_block;
-    float* sgf = sgi + chunk;
+    float* s_keep = sv + chunk * cols_per_block;  // exp(f_t + m_{t-1} - m_t)
+    float* s_take = s_keep + chunk;               // exp(i_t - m_t)
+    float* s_einv = s_take + chunk;               // exp(-m_t); then one float: m after the chunk
     const int n_qk = cn * dim;
+    if (vec8) {
+      // bfloat16 rows that allow 16-byte pieces: a thread moves 8 neighbouring elements of q and of k per load
+      const int per_tok = dim >> 3, n8 = cn * per_tok;
+      for (int g0 = tid; g0 < n8; g0 += MLSTM_THREADS * 4) {
+        uint4 rq[4], rk[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int g = g0 + j * MLSTM_THREADS;
+          if (g < n8) {
+            const int t = g / per_tok, r = (g - t * per_tok) << 3;
+            const T* row = qkv + (long long)(c0 + t) * row_stride + head * dim + r;
+            rq[j] = *reinterpret_cast<const uint4*>(row + q_off);
+            rk[j] = *reinterpret_cast<const uint4*>(row + k_off);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int g = g0 + j * MLSTM_THREADS;
+          if (g < n8) {
+            const __nv_bfloat16* eq = reinterpret_cast<const __nv_bfloat16*>(&rq[j]);
+            const __nv_bfloat16* ek = reinterpret_cast<const __nv_bfloat16*>(&rk[j]);
+            float4 a, b, c, d;
+            a.x = __bfloat162float(eq[0]) * q_scale, a.y = __bfloat162float(eq[1]) * q_scale;
+            a.z = __bfloat162float(eq[2]) * q_scale, a.w = __bfloat162float(eq[3]) * q_scale;
+            b.x = __bfloat162float(eq[4]) * q_scale, b.y = __bfloat162float(eq[5]) * q_scale;
+            b.z = __bfloat162float(eq[6]) * q_scale, b.w = __bfloat162float(eq[7]) * q_scale;
+            c.x = __bfloat162float(ek[0]), c.y = __bfloat162float(ek[1]), c.z = __bfloat162float(ek[2]), c.w = __bfloat162float(ek[3]);
+            d.x = __bfloat162float(ek[4]), d.y = __bfloat162float(ek[5]), d.z = __bfloat162float(ek[6]), d.w = __bfloat162float(ek[7]);
+            const int t = g / per_tok, e = t * dim + ((g - t * per_tok) << 3);
+            *reinterpret_cast<float4*>(sq + e) = a;
+            *reinterpret_cast<float4*>(sq + e + 4) = b;
+            *reinterpret_cast<float4*>(sk + e) = c;
+            *reinterpret_cast<float4*>(sk + e + 4) = d;
+          }
+        }
+      }
+    } else
     for (int e0 = tid; e0 < n_qk; e0 += MLSTM_THREADS * 8) {
       float tq[8], tk[8];
 #pragma unroll
@@ -112,23 +167,35 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
         if (e < n_v) sv[e] = tv[j];
       }
     }
-    if (tid < cn) {
-      const float* g = gates + (long long)(c0 + tid) * 2 * heads;
-      sgi[tid] = cap * tanhf((g[head] + bi) / cap);
-      sgf[tid] = log_sigmoid(cap * tanhf((g[heads + head] + bf) / cap));
+    // The gates and the running maximum of the chunk: a scan of a few tokens, by one warp of the stagers (the
+    // lanes evaluate the gates side by side, lane 0 runs the maximum along), so that the recurrence itself is
+    // left with multiply-adds.  `m_run` carries the maximum from chunk to chunk (it starts at the state's).
+    if (tid < 32) {
+      float gi = 0.f, gf = 0.f;
+      if (tid < cn) {
+        const float* g = gates + (long long)(c0 + tid) * 2 * heads;
+        gi = cap * tanhf((g[head] + bi) / cap);
+        gf = log_sigmoid(cap * tanhf((g[heads + head] + bf) / cap));
+      }
+      for (int t = 0; t < cn; ++t) {
+        const float ii = __shfl_sync(0xffffffffu, gi, t), fi = __shfl_sync(0xffffffffu, gf, t);
+        const float m_new = fmaxf(fi + m_run, ii);
+        if (tid == 0) {
+          s_keep[t] = expf(fi + m_run - m_new);
+          s_take[t] = expf(ii - m_new);
+          s_einv[t] = expf(-m_new);
+        }
+        m_run = m_new;
+      }
+      if (tid == 0) s_einv[chunk] = m_run;
     }
   };
 
-  float* st_row = state + (long long)slot * state_stride;
-  float* st_S = st_row + ((long long)head * vdim + (col_ok ? col : 0)) * dim;
-  float* st_n = st_row + (long long)heads * vdim * dim + (long long)head * dim;
-  float* st_m = st_row + (long long)heads * vdim * dim + (long long)heads * dim + head;
-
-  float S[MLSTM_RPT], n[MLSTM_RPT];
+  float S[RPT], n[RPT];
   float m = 0.f;
   if (!loader) {
 #pragma unroll
-    for (int i = 0; i < MLSTM_RPT; ++i) {
+    for (int i = 0; i < RPT; ++i) {
       const int r = lane_row + rs * i;
       const bool on = r < dim;
       S[i] = (on && col_ok) ? st_S[r] : 0.f;
@@ -149,28 +216,27 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
       const float* sq = sm + which * buf_floats;
       const float* sk = sq + chunk * dim;
       const float* sv = sk + chunk * dim;
-      const float* sgi = sv + chunk * cols_per_block;
-      const float* sgf = sgi + chunk;
+      const float* s_keep = sv + chunk * cols_per_block;
+      const float* s_take = s_keep + chunk;
+      const float* s_einv = s_take + chunk;
+#pragma unroll 2
       for (int t = 0; t < cn; ++t) {
-        const float fi = sgf[t], ii = sgi[t];
-        const float m_new = fmaxf(fi + m, ii);
-        const float keep = expf(fi + m - m_new), take = expf(ii - m_new);
-        m = m_new;
+        const float keep = s_keep[t], take = s_take[t];
         const float tv = take * sv[t * cols_per_block + col_in_block];
         const float* kq = sk + t * dim;
         const float* qq = sq + t * dim;
         float dot = 0.f, ndot = 0.f, dot2 = 0.f, ndot2 = 0.f;
 #pragma unroll
-        for (int i = 0; i < MLSTM_RPT; i += 2) {
+        for (int i = 0; i < RPT; i += 2) {
           const int r = lane_row + rs * i, r2 = r + rs;
-          if (r < dim) {
+          if (FULL || r < dim) {
             const float kr = kq[r], qr = qq[r];
             S[i] = fmaf(keep, S[i], kr * tv);
             n[i] = fmaf(keep, n[i], take * kr);
             dot = fmaf(S[i], qr, dot);
             ndot = fmaf(n[i], qr, ndot);
           }
-          if (r2 < dim) {
+          if (FULL || r2 < dim) {
             const float kr = kq[r2], qr = qq[r2];
             S[i + 1] = fmaf(keep, S[i + 1], kr * tv);
             n[i + 1] = fmaf(keep, n[i + 1], take * kr);
@@ -180,21 +246,30 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
         }
         dot += dot2;
         ndot += ndot2;
-        for (int o = rs >> 1; o > 0; o >>= 1) {
-          dot += __shfl_xor_sync(0xffffffffu, dot, o);
-          ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
+        if (FULL) {
+#pragma unroll
+          for (int o = RS >> 1; o > 0; o >>= 1) {
+            dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
+          }
+        } else {
+          for (int o = rs >> 1; o > 0; o >>= 1) {
+            dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
+          }
         }
         if (lane_row == 0 && col_ok) {
-          const float den = fmaxf(fabsf(ndot), expf(-m)) + 1e-6f;
+          const float den = fmaxf(fabsf(ndot), s_einv[t]) + 1e-6f;
           out[((long long)(c0 + t) * heads + head) * vdim + col] = dot / den;
         }
       }
+      m = s_einv[chunk];
     }
     __syncthreads();  // the next chunk is staged, this one used up
   }
   if (loader) return;
 #pragma unroll
-  for (int i = 0; i < MLSTM_RPT; ++i) {
+  for (int i = 0; i < RPT; ++i) {
     const int r = lane_row + rs * i;
     if (r < dim) {
       if (col_ok) st_S[r] = S[i];
@@ -228,9 +303,11 @@ __global__ void mlstm_out_gate_kernel(const float* __restrict__ o, const T* __re
   }
 }
 
+// Lanes that share a column: as many as leave a thread about 8 rows (the per-token chain of a thread is what
+// paces the recurrence, and narrower column tiles make more blocks), at most a warp.
 static int mlstm_rs(int dim) {
   int rs = 1;
-  while (rs * MLSTM_RPT < dim) rs <<= 1;
+  while (rs < 32 && rs * 8 < dim) rs <<= 1;
   return rs;
 }
 
@@ -253,12 +330,21 @@ static int mlstm_launch(const void* qkv, long long row_stride, int q_off, int k_
   const int cols = MLSTM_THREADS / rs;
   // tokens per staged chunk: two buffers of (2 dim + cols + 2) floats a token stay below 48 KB
   int chunk = 16;
-  while (chunk > 1 && (size_t)2 * chunk * (2 * dim + cols + 2) * sizeof(float) > 46 * 1024) chunk >>= 1;
-  const size_t smem = (size_t)2 * (2 * chunk * dim + chunk * cols + 2 * chunk) * sizeof(float);
+  while (chunk > 1 && (size_t)2 * chunk * (2 * dim + cols + 3) * sizeof(float) > 46 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * ((2 * chunk * dim + chunk * cols + 3 * chunk + 1 + 3) & ~3) * sizeof(float);
   const dim3 grid((vdim + cols - 1) / cols, heads, requests);
-  return ullm_launch_kernel(mlstm_recurrence_kernel<T>, grid, dim3(2 * MLSTM_THREADS), smem, st, (const T*)qkv,
-                            row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state, state_stride, cu_q,
-                            req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale, cap, num_slots, status);
+#define MLSTM_LAUNCH(RPT_, RS_)                                                                                       \
+  return ullm_launch_kernel(mlstm_recurrence_kernel<T, RPT_, RS_>, grid, dim3(2 * MLSTM_THREADS), smem, st,            \
+                            (const T*)qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state, state_stride, \
+                            cu_q, req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale, cap, num_slots,      \
+                            status)
+  if (dim == 64 && rs == 8) MLSTM_LAUNCH(8, 8);
+  if (dim == 128 && rs == 16) MLSTM_LAUNCH(8, 16);
+  if (dim == 256 && rs == 32) MLSTM_LAUNCH(8, 32);
+  if (dim == 512 && rs == 32) MLSTM_LAUNCH(16, 32);
+  if (rs * 8 >= dim) MLSTM_LAUNCH(8, 0);
+  MLSTM_LAUNCH(MLSTM_RPT, 0);
+#undef MLSTM_LAUNCH
 }
 
 // qkv: rows of `row_stride` elements that hold q [heads, dim] at q_off, k [heads, dim] at k_off and v [heads, vdim]
