@@ -525,8 +525,8 @@ def ludalix_config(width: int, heads: int, kv_heads: int, ff: int, experts: int,
                    dict(type="attention", mixer=dict(att), mlp=dict(moe)),
                    dict(type="attention", mixer=dict(att, kv_from=4 * g + 1), mlp=dict(moe)),
                    dict(type="mlstm", mixer=dict(st), mlp=dict(moe))]
-    return dict(architecture="Ludalix", vocab=vocab, width=width, residual_mult=0.7, embedding=dict(scale=16.0),
-                norm=dict(eps=1e-5), layers=layers, torch_dtype="bfloat16")
+    return dict(architecture="Ludalix", vocab=vocab, width=width, residual_mult=0.5, embedding=dict(scale=12.0),
+                norm=dict(eps=1e-6), layers=layers, torch_dtype="bfloat16")
 
 
 LUDALIX_SIZES = {
