@@ -34,7 +34,9 @@ __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - l
 // RPT: rows of S a thread holds at most (8 or MLSTM_RPT).  RS > 0: the lanes per column are known when the kernel
 // is compiled and dim == RS * RPT exactly, so the row loop has neither bounds checks nor address arithmetic left
 // (measured at dim 128: 2.5 times fewer instructions per token); RS == 0: any dim, lanes per column in `rs_arg`.
-template <typename T, int RPT, int RS>
+// CPT: neighbouring value columns a thread holds (1 or 4): the k and q a thread reads from shared memory and its
+// share of n serve all of them, which is what the multiply-adds wait for otherwise.
+template <typename T, int RPT, int RS, int CPT>
 __global__ void __launch_bounds__(2 * MLSTM_THREADS)
 mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off, int k_off, int v_off,
                         const float* __restrict__ gates, const float* __restrict__ bias_i,
@@ -50,12 +52,12 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
   pdl_launch_dependents();
   pdl_wait();
   const int req = blockIdx.z, head = blockIdx.y;
-  const int cols_per_block = MLSTM_THREADS / rs;
+  const int cols_per_block = (MLSTM_THREADS / rs) * CPT;
   const bool loader = threadIdx.x >= MLSTM_THREADS;
   const int tid = threadIdx.x & (MLSTM_THREADS - 1);
   const int lane_row = tid % rs;          // which rows: lane_row, lane_row + rs, ...
   const int col_in_block = tid / rs;
-  const int col = blockIdx.x * cols_per_block + col_in_block;
+  const int col = blockIdx.x * cols_per_block + col_in_block * CPT;  // the thread's first column
   const bool col_ok = col < vdim;
   const int t0 = cu_q[req], t1 = cu_q[req + 1];
   if (t1 <= t0) return;
@@ -66,8 +68,10 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
     return;
   }
   if (padding) {
-    if (!loader && lane_row == 0 && col_ok)
-      for (int t = t0; t < t1; ++t) out[((long long)t * heads + head) * vdim + col] = 0.f;
+    if (!loader && lane_row == 0)
+      for (int t = t0; t < t1; ++t)
+        for (int c = 0; c < CPT; ++c)
+          if (col + c < vdim) out[((long long)t * heads + head) * vdim + col + c] = 0.f;
     return;
   }
   const int buf_floats = (2 * chunk * dim + chunk * cols_per_block + 3 * chunk + 1 + 3) & ~3;  // (16-byte steps)
@@ -76,7 +80,7 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
   const float bi = bias_i != nullptr ? bias_i[head] : 0.f, bf = bias_f != nullptr ? bias_f[head] : 0.f;
 
   float* st_row = state + (long long)slot * state_stride;
-  float* st_S = st_row + ((long long)head * vdim + (col_ok ? col : 0)) * dim;
+  float* st_S = st_row + ((long long)head * vdim + (col_ok ? col : 0)) * dim;  // column c of the thread: + c * dim
   float* st_n = st_row + (long long)heads * vdim * dim + (long long)head * dim;
   float* st_m = st_row + (long long)heads * vdim * dim + (long long)heads * dim + head;
 
@@ -191,14 +195,15 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
     }
   };
 
-  float S[RPT], n[RPT];
+  float S[RPT][CPT], n[RPT];
   float m = 0.f;
   if (!loader) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
       const int r = lane_row + rs * i;
       const bool on = r < dim;
-      S[i] = (on && col_ok) ? st_S[r] : 0.f;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) S[i][c] = (on && col + c < vdim) ? st_S[(long long)c * dim + r] : 0.f;
       n[i] = on ? st_n[r] : 0.f;
     }
     m = *st_m;
@@ -222,45 +227,50 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
 #pragma unroll 2
       for (int t = 0; t < cn; ++t) {
         const float keep = s_keep[t], take = s_take[t];
-        const float tv = take * sv[t * cols_per_block + col_in_block];
+        float tv[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) tv[c] = take * sv[t * cols_per_block + col_in_block * CPT + c];
         const float* kq = sk + t * dim;
         const float* qq = sq + t * dim;
-        float dot = 0.f, ndot = 0.f, dot2 = 0.f, ndot2 = 0.f;
+        float dot[2][CPT], ndot[2] = {0.f, 0.f};  // rows of even and of odd index into sums of their own
 #pragma unroll
-        for (int i = 0; i < RPT; i += 2) {
-          const int r = lane_row + rs * i, r2 = r + rs;
+        for (int c = 0; c < CPT; ++c) dot[0][c] = dot[1][c] = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const int r = lane_row + rs * i;
           if (FULL || r < dim) {
             const float kr = kq[r], qr = qq[r];
-            S[i] = fmaf(keep, S[i], kr * tv);
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+              S[i][c] = fmaf(keep, S[i][c], kr * tv[c]);
+              dot[i & 1][c] = fmaf(S[i][c], qr, dot[i & 1][c]);
+            }
             n[i] = fmaf(keep, n[i], take * kr);
-            dot = fmaf(S[i], qr, dot);
-            ndot = fmaf(n[i], qr, ndot);
-          }
-          if (FULL || r2 < dim) {
-            const float kr = kq[r2], qr = qq[r2];
-            S[i + 1] = fmaf(keep, S[i + 1], kr * tv);
-            n[i + 1] = fmaf(keep, n[i + 1], take * kr);
-            dot2 = fmaf(S[i + 1], qr, dot2);
-            ndot2 = fmaf(n[i + 1], qr, ndot2);
+            ndot[i & 1] = fmaf(n[i], qr, ndot[i & 1]);
           }
         }
-        dot += dot2;
-        ndot += ndot2;
+        float nd = ndot[0] + ndot[1];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) dot[0][c] += dot[1][c];
         if (FULL) {
 #pragma unroll
           for (int o = RS >> 1; o > 0; o >>= 1) {
-            dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) dot[0][c] += __shfl_xor_sync(0xffffffffu, dot[0][c], o);
+            nd += __shfl_xor_sync(0xffffffffu, nd, o);
           }
         } else {
           for (int o = rs >> 1; o > 0; o >>= 1) {
-            dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            ndot += __shfl_xor_sync(0xffffffffu, ndot, o);
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) dot[0][c] += __shfl_xor_sync(0xffffffffu, dot[0][c], o);
+            nd += __shfl_xor_sync(0xffffffffu, nd, o);
           }
         }
-        if (lane_row == 0 && col_ok) {
-          const float den = fmaxf(fabsf(ndot), s_einv[t]) + 1e-6f;
-          out[((long long)(c0 + t) * heads + head) * vdim + col] = dot / den;
+        if (lane_row == 0) {
+          const float den = fmaxf(fabsf(nd), s_einv[t]) + 1e-6f;
+#pragma unroll
+          for (int c = 0; c < CPT; ++c)
+            if (col + c < vdim) out[((long long)(c0 + t) * heads + head) * vdim + col + c] = dot[0][c] / den;
         }
       }
       m = s_einv[chunk];
@@ -272,7 +282,9 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
   for (int i = 0; i < RPT; ++i) {
     const int r = lane_row + rs * i;
     if (r < dim) {
-      if (col_ok) st_S[r] = S[i];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c)
+        if (col + c < vdim) st_S[(long long)c * dim + r] = S[i][c];
       if (blockIdx.x == 0 && col_in_block == 0) st_n[r] = n[i];
     }
   }
@@ -327,17 +339,41 @@ static int mlstm_launch(const void* qkv, long long row_stride, int q_off, int k_
                         int heads, int dim, int vdim, float q_scale, float cap, int num_slots, int* status,
                         cudaStream_t st) {
   const int rs = mlstm_rs(dim);
-  const int cols = MLSTM_THREADS / rs;
+  // four (or two) columns per thread where that still leaves the SMs about two blocks each (fewer, fatter blocks: less
+  // q / k staging, several multiply-add chains per row read: head size 256 x 512, one prompt of 2,048 tokens,
+  // 13.6 -> 5.7 ms for four layers; but 256 values wide at one request, 64 blocks of four columns were slower
+  // than 256 of one)
+  int cpt = 1;
+  for (int c = 4; c > 1; c >>= 1) {
+    const int tile = (MLSTM_THREADS / rs) * c;
+    if (vdim >= tile && (long long)((vdim + tile - 1) / tile) * heads * requests >= 250) {
+      cpt = c;
+      break;
+    }
+  }
+  const int cols = (MLSTM_THREADS / rs) * cpt;
   // tokens per staged chunk: two buffers of (2 dim + cols + 2) floats a token stay below 48 KB
   int chunk = 16;
   while (chunk > 1 && (size_t)2 * chunk * (2 * dim + cols + 3) * sizeof(float) > 46 * 1024) chunk >>= 1;
   const size_t smem = (size_t)2 * ((2 * chunk * dim + chunk * cols + 3 * chunk + 1 + 3) & ~3) * sizeof(float);
   const dim3 grid((vdim + cols - 1) / cols, heads, requests);
 #define MLSTM_LAUNCH(RPT_, RS_)                                                                                       \
-  return ullm_launch_kernel(mlstm_recurrence_kernel<T, RPT_, RS_>, grid, dim3(2 * MLSTM_THREADS), smem, st,            \
-                            (const T*)qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state, state_stride, \
-                            cu_q, req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale, cap, num_slots,      \
-                            status)
+  do {                                                                                                                \
+    if (cpt == 4)                                                                                                     \
+      return ullm_launch_kernel(mlstm_recurrence_kernel<T, RPT_, RS_, 4>, grid, dim3(2 * MLSTM_THREADS), smem, st,     \
+                                (const T*)qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state,         \
+                                state_stride, cu_q, req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale,   \
+                                cap, num_slots, status);                                                              \
+    if (cpt == 2)                                                                                                     \
+      return ullm_launch_kernel(mlstm_recurrence_kernel<T, RPT_, RS_, 2>, grid, dim3(2 * MLSTM_THREADS), smem, st,     \
+                                (const T*)qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state,         \
+                                state_stride, cu_q, req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale,   \
+                                cap, num_slots, status);                                                              \
+    return ullm_launch_kernel(mlstm_recurrence_kernel<T, RPT_, RS_, 1>, grid, dim3(2 * MLSTM_THREADS), smem, st,       \
+                              (const T*)qkv, row_stride, q_off, k_off, v_off, gates, bias_i, bias_f, state,           \
+                              state_stride, cu_q, req_slots, token_req, out, heads, dim, vdim, rs, chunk, q_scale,     \
+                              cap, num_slots, status);                                                                \
+  } while (0)
   if (dim == 64 && rs == 8) MLSTM_LAUNCH(8, 8);
   if (dim == 128 && rs == 16) MLSTM_LAUNCH(8, 16);
   if (dim == 256 && rs == 32) MLSTM_LAUNCH(8, 32);
