@@ -161,7 +161,8 @@ def test_feed_forwards_alone(tmp_path, dtype):
 def test_routed_experts_on_tensor_cores_agree_with_the_plain_grouped_product(tmp_path):
     """Sizes that allow 16-byte pieces take the tensor-core grouped product in bfloat16; the same step with that
     kernel switched off must give the same rows up to the order of additions, and both follow the plain model.
-    200 tokens over 5 experts: tiles of 64 places with ragged ends, and an expert's columns that end inside a tile."""
+    300 and 90 tokens over 5 experts: tiles of 64 places with ragged ends, and an expert's columns that end inside
+    a tile."""
     from ullm_b200.csrc import kernels
     from ullm_b200.engine.batch import Workspace
 
@@ -170,22 +171,24 @@ def test_routed_experts_on_tensor_cores_agree_with_the_plain_grouped_product(tmp
     r = make_runner(tmp_path, cfg, w, 8, "bfloat16")
 
     class Ctx:
-        workspace = Workspace(r.device, max_tokens=256, max_requests=4)
+        workspace = Workspace(r.device, max_tokens=320, max_requests=4)
 
-    x = rand((200, 72), 3, "bfloat16", 1.5)
     ff = r.model.blocks[0].feed_forward
-    fast = ff.forward(x.clone(), Ctx()).float().cpu().clone()
-    kernels().moe_force_plain(True)
-    try:
-        slow = ff.forward(x.clone(), Ctx()).float().cpu().clone()
-    finally:
-        kernels().moe_force_plain(False)
-    assert (fast - slow).abs().max() <= 2e-2 * slow.abs().max()
-    ref = pl.feed_forward(x.double().cpu(), {n: t.double() for n, t in w.items()}, "l0.mlp.", cfg["layers"][0]["mlp"]).float()
-    s = torch.sigmoid(x.double().cpu() @ w["l0.mlp.router"].double().T).sort(-1, descending=True).values
-    clear = (s[:, 1] - s[:, 2]) > 0.005
-    assert clear.sum() > 150
-    assert_close(fast[clear], ref[clear], "bfloat16", "routed experts on tensor cores")
+    for rows in (300, 90):
+        x = rand((rows, 72), 3 + rows, "bfloat16", 1.5)
+        fast = ff.forward(x.clone(), Ctx()).float().cpu().clone()
+        kernels().moe_force_plain(True)
+        try:
+            slow = ff.forward(x.clone(), Ctx()).float().cpu().clone()
+        finally:
+            kernels().moe_force_plain(False)
+        assert (fast - slow).abs().max() <= 2e-2 * slow.abs().max()
+        ref = pl.feed_forward(x.double().cpu(), {n: t.double() for n, t in w.items()}, "l0.mlp.",
+                              cfg["layers"][0]["mlp"]).float()
+        s = torch.sigmoid(x.double().cpu() @ w["l0.mlp.router"].double().T).sort(-1, descending=True).values
+        clear = (s[:, 1] - s[:, 2]) > 0.005
+        assert clear.sum() > 0.75 * rows
+        assert_close(fast[clear], ref[clear], "bfloat16", f"routed experts on tensor cores, {rows} rows")
 
 
 def test_router_weight_multiplies_the_experts_input_not_its_output():
