@@ -400,3 +400,33 @@ def test_greedy_generation_through_the_entry_point(tmp_path, tag, eager):
                 assert tok == int(torch.argmax(lg)), f"prompt of {len(p)}: token {len(seq) - len(p)} differs"
             seq.append(tok)
     llm.engine.runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("eager", [True, False])
+def test_preempted_requests_start_again_from_zeroed_state(tmp_path, eager):
+    """A pool too small for three requests of about 60 tokens: some are preempted, take a slot again later (their
+    state rows zeroed, their prompt and generated tokens recomputed) and still produce the plain model's tokens."""
+    from ludalix_helpers import write_model
+    from ullm_b200 import LLM, EngineConfig, SamplingParams
+
+    cfg, w, page = weights_for("Q", "float32")
+    d = write_model(str(tmp_path / f"pre{eager}"), cfg, w)
+    ec = EngineConfig(model=d, max_bs=3, context_len=96, page_size=page, num_pages=34, max_num_batched_tokens=32,
+                      dtype="float32", enforce_eager=eager)
+    if device() == "cpu":
+        type(ec).device = property(lambda self: "cpu")
+    llm = LLM(ec)
+    prompts = [random_ids(cfg["vocab"], n, 200 + n) for n in (30, 22, 35)]
+    outs = llm.generate_batch(prompts, SamplingParams(temperature=0.0, max_new_tokens=30, ignore_eos=True))
+    assert llm.engine.stats()["preemptions"] >= 1, "34 pages of 4 tokens cannot hold three requests of 52 to 65 tokens"
+    wd = {n: t.double() for n, t in w.items()}
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 30
+        seq = list(p)
+        for tok in o.token_ids:
+            lg = pl.forward_logits(seq, wd, cfg)[-1]
+            top2 = torch.topk(lg, 2).values
+            if top2[0] - top2[1] > 1e-3 * lg.abs().max():
+                assert tok == int(torch.argmax(lg)), f"prompt of {len(p)}: token {len(seq) - len(p)} differs"
+            seq.append(tok)
+    llm.engine.runner.cache.check_invariants()
