@@ -65,7 +65,15 @@ CFG_S = config(96, 77, [
     ("mlstm", mlstm(1, 256, 136, 9.0), None),
 ], mult=0.7, scale=5.0)
 
-CONFIGS = {"P": (CFG_P, 8), "Q": (CFG_Q, 4), "R": (CFG_R, 16), "S": (CFG_S, 16)}  # config, page size
+# T: windows without kept tokens at the head sizes of the tensor-core attention kernels (the paths the rotary
+# models take, here without any rotation), one of them read again by a later layer under another window
+CFG_T = config(96, 150, [
+    ("attention", attention(4, 2, 128, 128, 40, 0, 0.09), dense(72, 4.0)),
+    ("attention", attention(2, 2, 64, 64, 24, 0, 0.125), None),
+    ("attention", attention(4, 2, 128, 128, 100, 0, 0.09, kv_from=0), moe(4, 2, 40)),
+], mult=0.65, scale=6.0)
+
+CONFIGS = {"P": (CFG_P, 8), "Q": (CFG_Q, 4), "R": (CFG_R, 16), "S": (CFG_S, 16), "T": (CFG_T, 16)}  # config, page size
 
 
 def weights_for(tag: str, dtype: str, seed: int = 0, std_scale: float = 1.0):
