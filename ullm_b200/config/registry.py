@@ -22,13 +22,16 @@ class Architecture:
     name: str
     parse_config: Callable[[dict[str, Any]], Any]  # config.json dict -> typed config
     model_spec: Callable[[Any], ModelSpec]  # typed config -> ModelSpec
+    # True: a size of the design is given by a tensor's shape and not by a config.json key; `parse_config` then
+    # takes a second argument, {tensor name: shape} of the model folder's files (None for a bare config dict)
+    reads_shapes: bool = False
 
 
 ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config, model_spec) -> Architecture:
-    arch = Architecture(name, parse_config, model_spec)
+def register_architecture(name: str, parse_config, model_spec, reads_shapes: bool = False) -> Architecture:
+    arch = Architecture(name, parse_config, model_spec, reads_shapes)
     ARCHITECTURES[name] = arch
     return arch
 
@@ -58,7 +61,20 @@ def load_model_spec(model_dir_or_dict) -> tuple[Any, ModelSpec]:
     """(typed config, ModelSpec) for a model folder or a config.json dict."""
     d = model_dir_or_dict if isinstance(model_dir_or_dict, dict) else read_config_json(model_dir_or_dict)
     arch = resolve_architecture(d)
-    cfg = arch.parse_config(d)
+    if arch.reads_shapes:
+        shapes = None
+        if not isinstance(model_dir_or_dict, dict):
+            from ..weights.safetensors_io import open_model_files
+
+            files = open_model_files(model_dir_or_dict)
+            try:
+                shapes = {n: tuple(f.shape(n)) for f in files for n in f.names()}
+            finally:
+                for f in files:
+                    f.close()
+        cfg = arch.parse_config(d, shapes)
+    else:
+        cfg = arch.parse_config(d)
     spec = arch.model_spec(cfg)
     spec.validate()
     return cfg, spec

@@ -78,6 +78,16 @@ class ScheduleEntry:
     cache_of: int | None = None
 
 
+@dataclass(frozen=True)
+class TokenSideSpec:
+    """A second embedding table [vocab, shares * dim] of which every layer reads a share of `dim` columns of its
+    tokens' rows (a per-layer token input).  `name`: the table's tensor name."""
+
+    name: str
+    dim: int
+    shares: int
+
+
 @dataclass
 class ModelSpec:
     architecture: str
@@ -103,6 +113,10 @@ class ModelSpec:
     # "engine": the residual stream has the engine's dtype; "float32": it is kept in 32-bit whatever the engine's
     # dtype (the blocks of such a model take and return a 32-bit stream)
     stream_dtype: str = "engine"
+    # logits <- logit_softcap * tanh(logits / logit_softcap) when set
+    logit_softcap: float | None = None
+    # a per-layer token input table that blocks read through the step's context (`ctx.token_side`)
+    token_side: TokenSideSpec | None = None
 
     def validate(self) -> None:
         if not self.layers:

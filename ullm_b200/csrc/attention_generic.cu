@@ -34,23 +34,35 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
                                                const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                                const int* __restrict__ token_req, int tokens, int num_q, int num_kv,
                                                int head_dim, int page_size, int window, float scale,
-                                               long long num_pages, int* status, int v_dim, int keep_first) {
+                                               long long num_pages, int* status, int v_dim, int keep_first,
+                                               float softcap, int v_rep, float* __restrict__ out_f32) {
   __shared__ float qs[ATT_WARPS][ATT_MAX_HEAD_DIM];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * ATT_WARPS + warp;
-  if (unit >= (long long)tokens * num_q) return;
-  const int t = (int)(unit / num_q);
-  const int h = (int)(unit - (long long)t * num_q);
+  // v_rep == 1: one unit per (token, query head), which reads the values of its own kv head.  v_rep == num_kv:
+  // a unit per (token, query head, VALUE head): head h's softmax weights applied to every kv head's values
+  // (what mixing the weights across heads needs); the results are 32-bit rows [token][head][value head].
+  const int units_per_token = num_q * v_rep;
+  if (unit >= (long long)tokens * units_per_token) return;
+  const int t = (int)(unit / units_per_token);
+  const int hu = (int)(unit - (long long)t * units_per_token);
+  const int h = hu / v_rep;
   const int kh = h / (num_q / num_kv);
-  T* o_ptr = out + ((long long)t * num_q + h) * v_dim;
+  const int vh = v_rep > 1 ? hu - h * v_rep : kh;
+  T* o_ptr = out_f32 == nullptr ? out + ((long long)t * units_per_token + hu) * v_dim : nullptr;
+  float* o32 = out_f32 != nullptr ? out_f32 + ((long long)t * units_per_token + hu) * v_dim : nullptr;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   const int r = token_req[t];
   const int q_len = r >= 0 ? cu_q[r + 1] - cu_q[r] : 0;
   const int kvl = r >= 0 ? kv_len[r] : 0;
   const int pos = kvl - q_len + (r >= 0 ? t - cu_q[r] : 0);
   if (r < 0 || q_len <= 0 || kvl <= 0 || pos < 0) {  // padding row
-    for (int e = lane; e < v_dim; e += 32) o_ptr[e] = from_f32<T>(0.f);
+    for (int e = lane; e < v_dim; e += 32) {
+      if (o32 != nullptr) o32[e] = 0.f;
+      else o_ptr[e] = from_f32<T>(0.f);
+    }
     return;
   }
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -85,6 +97,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
         float d = 0.f;
         for (int e = 0; e < head_dim; ++e) d += qv[e] * to_f32(kp[e]);
         s = d * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -98,7 +111,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const long long sj = __shfl_sync(0xffffffffu, slot, j);
       if (sj < 0) continue;
-      const T* vp = v_cache + sj * v_row + (long long)kh * v_dim;
+      const T* vp = v_cache + sj * v_row + (long long)vh * v_dim;
 #pragma unroll
       for (int i = 0; i < OREGS; ++i) {
         const int e = lane + 32 * i;
@@ -112,8 +125,32 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
 #pragma unroll
   for (int i = 0; i < OREGS; ++i) {
     const int e = lane + 32 * i;
-    if (e < v_dim) o_ptr[e] = from_f32<T>(acc[i] * inv);
+    if (e < v_dim) {
+      if (o32 != nullptr) o32[e] = acc[i] * inv;
+      else o_ptr[e] = from_f32<T>(acc[i] * inv);
+    }
   }
+}
+
+// Softmax weights mixed across heads, w'_h = sum_g M[h][g] w_g, applied to head h's own values:
+// out[t][h] = sum_g M[h][g] * part[t][g][kv head of h], with part = every head's weights applied to every kv
+// head's values (32-bit, from the kernel above with v_rep = num_kv).  One thread per output element.
+template <typename T>
+__global__ void mix_heads_kernel(const float* __restrict__ part, const float* __restrict__ mix, T* __restrict__ out,
+                                 long long total, int num_q, int num_kv, int v_dim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int e = (int)(i % v_dim);
+  const long long th = i / v_dim;
+  const int h = (int)(th % num_q);
+  const long long t = th / num_q;
+  const int kh = h / (num_q / num_kv);
+  const float* p = part + ((t * num_q) * num_kv + kh) * v_dim + e;
+  float acc = 0.f;
+  for (int g = 0; g < num_q; ++g) acc += mix[h * num_q + g] * p[(long long)g * num_kv * v_dim];
+  out[i] = from_f32<T>(acc);
 }
 
 template <typename T>
@@ -121,15 +158,15 @@ static int launch_generic(const void* q, long long q_row_stride, void* out, cons
                           const int* block_table, int max_pages, const int* req_slots, const int* cu_q,
                           const int* kv_len, const int* token_req, int tokens, int num_q, int num_kv, int head_dim, int page_size,
                           int window, float scale, long long num_pages, int* status, cudaStream_t st, int v_dim,
-                          int keep_first) {
-  const long long units = (long long)tokens * num_q;
+                          int keep_first, float softcap = 0.f, int v_rep = 1, float* out_f32 = nullptr) {
+  const long long units = (long long)tokens * num_q * v_rep;
   const long long blocks = (units + ATT_WARPS - 1) / ATT_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
 #define LAUNCH(OREGS)                                                                                             \
   rc = ullm_launch_kernel(paged_attention_generic_kernel<T, OREGS>, dim3((int)blocks), dim3(ATT_WARPS * 32), 0, st, \
       (const T*)q, q_row_stride, (T*)out, (const T*)k_cache, (const T*)v_cache, block_table, max_pages, req_slots,  \
       cu_q, kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status,       \
-      v_dim, keep_first)
+      v_dim, keep_first, softcap, v_rep, out_f32)
   int rc = ULLM_OK;
   if (v_dim <= 32) LAUNCH(1);
   else if (v_dim <= 64) LAUNCH(2);
@@ -138,6 +175,62 @@ static int launch_generic(const void* q, long long q_row_stride, void* out, cons
   else LAUNCH(16);
 #undef LAUNCH
   return rc;
+}
+
+// `v_dim`: head size of the values (and of the output); `keep_first`: positions below it stay visible;
+// `softcap` > 0: score <- softcap * tanh(score / softcap); `out_parts` (32-bit, [tokens][heads][kv heads][v_dim])
+// non-null: every head's weights are applied to EVERY kv head's values and left there unrounded (`out` unused),
+// for `ullm_mix_heads`.
+extern "C" int ullm_paged_attention_generic_ex2(int dtype, const void* q, long long q_row_stride, void* out,
+                                                const void* k_cache, const void* v_cache, const int* block_table,
+                                                int max_pages, const int* req_slots, const int* cu_q,
+                                                const int* kv_len, const int* token_req, int tokens, int num_q,
+                                                int num_kv, int head_dim, int page_size, int window, float scale,
+                                                long long num_pages, int* status, void* stream, int v_dim,
+                                                int keep_first, float softcap, float* out_parts) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
+    return ULLM_ERR_BAD_SIZE;
+  if (num_q % num_kv != 0 || head_dim > ATT_MAX_HEAD_DIM || window < 0 || v_dim <= 0 || v_dim > ATT_MAX_HEAD_DIM ||
+      keep_first < 0 || softcap < 0.f)
+    return ULLM_ERR_UNSUPPORTED;
+  if (tokens == 0) return ULLM_OK;
+  const int v_rep = out_parts != nullptr ? num_kv : 1;
+  if (dtype == ULLM_DTYPE_F32)
+    return launch_generic<float>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                 kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
+                                 status, st, v_dim, keep_first, softcap, v_rep, out_parts);
+  if (dtype == ULLM_DTYPE_BF16)
+    return launch_generic<__nv_bfloat16>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                         kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale,
+                                         num_pages, status, st, v_dim, keep_first, softcap, v_rep, out_parts);
+  if (dtype == ULLM_DTYPE_F16)
+    return launch_generic<__half>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                  kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
+                                  status, st, v_dim, keep_first, softcap, v_rep, out_parts);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// out [tokens][heads][v_dim] (the engine's dtype) = the parts mixed by `mix` [heads][heads] (32-bit).
+extern "C" int ullm_mix_heads(int dtype, const float* parts, const float* mix, void* out, int tokens, int num_q,
+                              int num_kv, int v_dim, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || num_q <= 0 || num_kv <= 0 || v_dim <= 0 || num_q % num_kv) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  const long long total = (long long)tokens * num_q * v_dim;
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
+  const dim3 grid((int)blocks), block(256);
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(mix_heads_kernel<float>, grid, block, 0, st, parts, mix, (float*)out, total, num_q,
+                              num_kv, v_dim);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(mix_heads_kernel<__nv_bfloat16>, grid, block, 0, st, parts, mix, (__nv_bfloat16*)out,
+                              total, num_q, num_kv, v_dim);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(mix_heads_kernel<__half>, grid, block, 0, st, parts, mix, (__half*)out, total, num_q,
+                              num_kv, v_dim);
+  return ULLM_ERR_BAD_DTYPE;
 }
 
 // `v_dim`: head size of the values (and of the output); `keep_first`: positions below it stay visible.

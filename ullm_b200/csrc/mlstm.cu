@@ -295,7 +295,7 @@ mlstm_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_o
 template <typename T>
 __global__ void mlstm_out_gate_kernel(const float* __restrict__ o, const T* __restrict__ g, long long g_stride,
                                       const float* __restrict__ w, T* __restrict__ out, long long units, int heads,
-                                      int vdim, float eps) {
+                                      int vdim, float eps, int w_per_head, int silu) {
   pdl_launch_dependents();
   pdl_wait();
   const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -310,8 +310,9 @@ __global__ void mlstm_out_gate_kernel(const float* __restrict__ o, const T* __re
   const float rstd = 1.f / sqrtf(ss / (float)vdim + eps);
   const T* gr = g + t * g_stride + (long long)h * vdim;
   for (int e = lane; e < vdim; e += 32) {
-    const float gate = 1.f / (1.f + expf(-to_f32(gr[e])));
-    out[unit * vdim + e] = from_f32<T>(src[e] * rstd * w[h * vdim + e] * gate);
+    const float gv = to_f32(gr[e]);
+    const float gate = (silu ? gv : 1.f) / (1.f + expf(-gv));
+    out[unit * vdim + e] = from_f32<T>(src[e] * rstd * w[(w_per_head ? h * vdim : 0) + e] * gate);
   }
 }
 
@@ -411,8 +412,11 @@ extern "C" int ullm_mlstm_recurrence(int dtype, const void* qkv, long long row_s
   return ULLM_ERR_BAD_DTYPE;
 }
 
-extern "C" int ullm_mlstm_out_gate(int dtype, const float* o, const void* g, long long g_stride, const float* w,
-                                   void* out, int tokens, int heads, int vdim, float eps, void* stream) {
+// Per (token, head): o / sqrt(mean(o^2) + eps) * w * gate(g), with w [heads * vdim] (`w_per_head`) or [vdim] shared
+// by the heads, and gate = sigmoid (`silu` 0) or silu (1).
+extern "C" int ullm_head_norm_gate(int dtype, const float* o, const void* g, long long g_stride, const float* w,
+                                   void* out, int tokens, int heads, int vdim, float eps, int w_per_head, int silu,
+                                   void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || heads <= 0 || vdim <= 0) return ULLM_ERR_BAD_SIZE;
   if (tokens == 0) return ULLM_OK;
@@ -422,12 +426,17 @@ extern "C" int ullm_mlstm_out_gate(int dtype, const float* o, const void* g, lon
   const dim3 grid((int)blocks), block(128);
   if (dtype == ULLM_DTYPE_F32)
     return ullm_launch_kernel(mlstm_out_gate_kernel<float>, grid, block, 0, st, o, (const float*)g, g_stride, w,
-                              (float*)out, units, heads, vdim, eps);
+                              (float*)out, units, heads, vdim, eps, w_per_head, silu);
   if (dtype == ULLM_DTYPE_BF16)
     return ullm_launch_kernel(mlstm_out_gate_kernel<__nv_bfloat16>, grid, block, 0, st, o, (const __nv_bfloat16*)g,
-                              g_stride, w, (__nv_bfloat16*)out, units, heads, vdim, eps);
+                              g_stride, w, (__nv_bfloat16*)out, units, heads, vdim, eps, w_per_head, silu);
   if (dtype == ULLM_DTYPE_F16)
     return ullm_launch_kernel(mlstm_out_gate_kernel<__half>, grid, block, 0, st, o, (const __half*)g, g_stride, w,
-                              (__half*)out, units, heads, vdim, eps);
+                              (__half*)out, units, heads, vdim, eps, w_per_head, silu);
   return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_mlstm_out_gate(int dtype, const float* o, const void* g, long long g_stride, const float* w,
+                                   void* out, int tokens, int heads, int vdim, float eps, void* stream) {
+  return ullm_head_norm_gate(dtype, o, g, g_stride, w, out, tokens, heads, vdim, eps, 1, 0, stream);
 }

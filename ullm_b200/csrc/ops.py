@@ -238,6 +238,17 @@ class Kernels:
             "ullm_cast_rows_f32": [I, P, P, LL, P],
             "ullm_mlstm_recurrence": [I, P, LL, I, I, I, P, P, P, P, LL, P, P, P, P, I, I, I, I, F, F, I, P, P],
             "ullm_mlstm_out_gate": [I, P, P, LL, P, P, I, I, I, F, P],
+            "ullm_gated_add_f32": [I, P, P, P, LL, P, P, P, P, I, I, P],
+            "ullm_side_gate_mul": [I, P, P, P, LL, I, P, I, I, I, P, P, P, P, P],
+            "ullm_softcap_f32": [P, LL, F, P],
+            "ullm_qkv_prepare": [I, P, LL, I, I, I, I, I, P, I, P, LL, P, P, P, I, P, P, I, P, P, I, I, F, I, P, P, P, P,
+                                 P, LL, P, P, P],
+            "ullm_conv_state_update": [I, P, LL, I, I, P, LL, P, P, P, I, I, P],
+            "ullm_paged_attention_generic_ex2": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I,
+                                                 F, P],
+            "ullm_mix_heads": [I, P, P, P, I, I, I, I, P],
+            "ullm_gla_recurrence": [I, P, LL, I, I, I, P, LL, P, F, F, P, LL, P, P, P, P, I, I, I, I, I, P, P],
+            "ullm_head_norm_gate": [I, P, P, LL, P, P, I, I, I, F, I, I, P],
             "ullm_moe_route": [P, P, P, I, I, I, I, I, P],
             "ullm_moe_arrange": [P, I, I, P, P, P, P],
             "ullm_moe_grouped_linear": [I, P, LL, P, LL, P, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -255,6 +266,10 @@ class Kernels:
         L.ullm_mlstm_supported.restype = c_int
         L.ullm_mlstm_state_floats.argtypes = [I, I, I]
         L.ullm_mlstm_state_floats.restype = c_longlong
+        L.ullm_gla_supported.argtypes = [I, I, I]
+        L.ullm_gla_supported.restype = c_int
+        L.ullm_gla_state_floats.argtypes = [I, I, I]
+        L.ullm_gla_state_floats.restype = c_longlong
         L.ullm_wait_selftest.argtypes = [I, P, P, P]
         L.ullm_wait_selftest.restype = c_int
         L.ullm_decode_attention_supported.argtypes = [I, I, I]
@@ -833,6 +848,183 @@ class Kernels:
         self._check(self.lib.ullm_mlstm_out_gate(_DT[out.dtype], _ptr(o), _ptr(g), g.stride(0), _ptr(weight), _ptr(out), T,
                                                  heads, vdim, float(eps), _stream()), "mlstm_out_gate")
 
+    @_timed("mlstm")
+    def head_norm_gate(self, o, g, weight, eps, out, heads, vdim, silu: bool = False):
+        """out = o / sqrt(mean over a head of o^2 + eps) * weight * gate(g); o float32 [T, heads * vdim], g a view
+        [T, heads * vdim] of the projection's rows (any row stride); weight [heads * vdim], or [vdim] shared by the
+        heads; gate = sigmoid, or silu when `silu`."""
+        _need(o, "o", torch.float32)
+        _need(g, "g", out.dtype, contiguous=False)
+        _need(weight, "weight", torch.float32)
+        _need(out, "out")
+        T = o.shape[0]
+        if (o.shape != (T, heads * vdim) or g.shape != o.shape or out.shape != o.shape or g.stride(1) != 1
+                or weight.numel() not in (vdim, heads * vdim)):
+            raise KernelError(f"head_norm_gate: o {tuple(o.shape)}, g {tuple(g.shape)}, out {tuple(out.shape)}, "
+                              f"weight {tuple(weight.shape)}")
+        per_head = int(weight.numel() == heads * vdim and heads > 1)
+        self._check(self.lib.ullm_head_norm_gate(_DT[out.dtype], _ptr(o), _ptr(g), g.stride(0), _ptr(weight), _ptr(out), T,
+                                                 heads, vdim, float(eps), per_head, int(bool(silu)), _stream()),
+                    "head_norm_gate")
+
+    # -- gated linear attention ---------------------------------------------------
+    def gla_supported(self, heads: int, dim: int, vdim: int) -> bool:
+        return bool(self.lib.ullm_gla_supported(heads, dim, vdim))
+
+    def gla_state_floats(self, heads: int, dim: int, vdim: int) -> int:
+        return int(self.lib.ullm_gla_state_floats(heads, dim, vdim))
+
+    @_timed("gla")
+    def gla_recurrence(self, qkv, q_off, k_off, v_off, z, z_bias, inv_tau, q_scale, state, cu_q, req_slots, token_req,
+                       out, requests, heads, dim, vdim):
+        """The recurrence of csrc/gla.cu over the step's tokens, from and into the requests' state rows.
+        qkv [T, *]: q, k, v at the given column offsets; z [T, heads * dim] float32 (the decay's projection, a view
+        with any row stride), `z_bias` float32 [heads * dim] or None; out [T, heads * vdim] float32."""
+        _need(qkv, "qkv")
+        _need(z, "z", torch.float32, contiguous=False)
+        _need(state, "state", torch.float32)
+        _need(out, "out", torch.float32)
+        if z_bias is not None:
+            _need(z_bias, "decay bias", torch.float32)
+        for t_, n_ in ((cu_q, "cu_q"), (req_slots, "req_slots"), (token_req, "token_req")):
+            _need(t_, n_, torch.int32)
+        T = qkv.shape[0]
+        if z.shape != (T, heads * dim) or z.stride(1) != 1 or out.shape != (T, heads * vdim) or state.dim() != 2:
+            raise KernelError(f"gla_recurrence: qkv {tuple(qkv.shape)}, z {tuple(z.shape)}, out {tuple(out.shape)}")
+        if max(q_off, k_off) + heads * dim > qkv.shape[1] or v_off + heads * vdim > qkv.shape[1]:
+            raise KernelError("gla_recurrence: q, k or v lie outside the rows")
+        if z_bias is not None and z_bias.numel() != heads * dim:
+            raise KernelError("gla_recurrence: the decay bias has the wrong length")
+        self._check(self.lib.ullm_gla_recurrence(
+            _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), q_off, k_off, v_off, _ptr(z), z.stride(0), _ptr(z_bias),
+            float(inv_tau), float(q_scale), _ptr(state), state.stride(0), _ptr(cu_q), _ptr(req_slots), _ptr(token_req),
+            _ptr(out), requests, heads, dim, vdim, state.shape[0], _ptr(self.status), _stream()),
+            f"gla_recurrence (heads {heads}, dim {dim}, vdim {vdim})")
+
+    # -- sub-layers added to a 32-bit stream through gates; a per-token side input ----------
+    @_timed("add_rmsnorm")
+    def gated_add_f32(self, a, f, gates, b1, b2, stream, copy=None):
+        """stream (float32, in place) += sigmoid(gates[:, :W] + b1) * a (+ sigmoid(gates[:, W:] + b2) * f when f is
+        given); `copy` (a's dtype, optional) gets the rounded stream.  gates float32 [T, W or 2 W]."""
+        _need(a, "a")
+        _need(gates, "gates", torch.float32)
+        _need(stream, "stream", torch.float32)
+        _need(b1, "b1", torch.float32)
+        T, W = a.shape
+        if stream.shape != a.shape or gates.shape != (T, W * (2 if f is not None else 1)) or b1.numel() != W:
+            raise KernelError(f"gated_add_f32: a {tuple(a.shape)}, gates {tuple(gates.shape)}, stream {tuple(stream.shape)}")
+        if f is not None:
+            _need(f, "f", a.dtype)
+            _need(b2, "b2", torch.float32)
+            if f.shape != a.shape or b2.numel() != W:
+                raise KernelError("gated_add_f32: the second sub-layer's shapes differ")
+        if copy is not None:
+            _need(copy, "copy", a.dtype)
+            if copy.shape != a.shape:
+                raise KernelError("gated_add_f32: the copy's shape differs")
+        self._check(self.lib.ullm_gated_add_f32(_DT[a.dtype], _ptr(a), _ptr(f), _ptr(gates), gates.stride(0), _ptr(b1),
+                                                _ptr(b2 if f is not None else None), _ptr(stream), _ptr(copy), T, W,
+                                                _stream()), "gated_add_f32")
+
+    @_timed("act_mul")
+    def side_gate_mul(self, s, ids, table, offset: int, out, last_tokens=None, token_req=None, req_slots=None):
+        """out[t] = gelu_tanh(s[t]) * table[ids[t], offset : offset + cols]; an id of -1 is the request's last
+        sampled token, as in `embedding`."""
+        _need(s, "s")
+        _need(ids, "ids", torch.int32)
+        _need(table, "table", s.dtype)
+        _need(out, "out", s.dtype)
+        T, C = s.shape
+        if out.shape != s.shape or ids.numel() < T or table.dim() != 2 or offset < 0 or offset + C > table.shape[1]:
+            raise KernelError(f"side_gate_mul: s {tuple(s.shape)}, table {tuple(table.shape)}, offset {offset}")
+        if last_tokens is not None:
+            for t_, n_ in ((last_tokens, "last_tokens"), (token_req, "token_req"), (req_slots, "req_slots")):
+                _need(t_, n_, torch.int32)
+        self._check(self.lib.ullm_side_gate_mul(_DT[s.dtype], _ptr(s), _ptr(ids), _ptr(table), table.stride(0), int(offset),
+                                                _ptr(out), T, C, table.shape[0], _ptr(last_tokens), _ptr(token_req),
+                                                _ptr(req_slots), _ptr(self.status), _stream()), "side_gate_mul")
+
+    @_timed("linear_head")
+    def softcap_f32(self, x, cap: float):
+        """x (float32, in place) = cap * tanh(x / cap)."""
+        _need(x, "x", torch.float32)
+        self._check(self.lib.ullm_softcap_f32(_ptr(x), x.numel(), float(cap), _stream()), "softcap_f32")
+
+    # -- between an attention's projection and its scores, in general form ----------------
+    @_timed("qk_norm_rope_store")
+    def qkv_prepare(self, qkv, q_out, num_q, num_kv, head_dim, v_dim, positions, slot_mapping, k_pages, v_pages, *,
+                    conv_w=None, taps: int = 0, conv_state=None, cu_q=None, token_req=None, req_slots=None,
+                    inv_freq=None, rotary_dim: int = 0, q_w=None, k_w=None, norm_first: bool = False,
+                    norm_last: bool = False, eps: float = 0.0, vmix_mode: int = 0, vmix_lambda=None, v_first=None):
+        """See csrc/attention_prep.cu: short convolution (with the requests' state rows), norm, rotation by computed
+        angles, unit norm, value mixing, cache stores; q goes to `q_out` [T, num_q * head_dim]."""
+        _need(qkv, "qkv")
+        _need(q_out, "q_out", qkv.dtype)
+        T, W = qkv.shape
+        if W != num_q * head_dim + num_kv * (head_dim + v_dim) or q_out.shape != (T, num_q * head_dim):
+            raise KernelError(f"qkv_prepare: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}")
+        for t_, n_ in ((token_req, "token_req"), (positions, "positions")):
+            _need(t_, n_, torch.int32)
+        state_stride = state_slots = 0
+        if conv_w is not None:
+            _need(conv_w, "conv_w", qkv.dtype)
+            if conv_w.shape != (W, taps):
+                raise KernelError(f"qkv_prepare: conv_w {tuple(conv_w.shape)} != ({W}, {taps})")
+            for t_, n_ in ((cu_q, "cu_q"), (req_slots, "req_slots")):
+                _need(t_, n_, torch.int32)
+            if taps > 1:
+                _need(conv_state, "conv_state", torch.float32)
+                if conv_state.dim() != 2 or conv_state.shape[1] < (taps - 1) * W:
+                    raise KernelError(f"qkv_prepare: conv_state {tuple(conv_state.shape)} is too small")
+                state_stride, state_slots = conv_state.stride(0), conv_state.shape[0]
+        for t_, n_ in ((inv_freq, "inv_freq"), (q_w, "q norm weight"), (k_w, "k norm weight"), (vmix_lambda, "vmix")):
+            if t_ is not None:
+                _need(t_, n_, torch.float32)
+        if rotary_dim > 0 and (inv_freq is None or inv_freq.numel() < rotary_dim // 2):
+            raise KernelError("qkv_prepare: the frequency table is too short")
+        if v_first is not None:
+            _need(v_first, "v_first", qkv.dtype)
+            if v_first.shape != (T, num_kv * v_dim):
+                raise KernelError(f"qkv_prepare: v_first {tuple(v_first.shape)} != ({T}, {num_kv * v_dim})")
+        num_slots = 0
+        if slot_mapping is not None:
+            _need(slot_mapping, "slot_mapping", torch.int32)
+            _need(k_pages, "k_pages", qkv.dtype)
+            _need(v_pages, "v_pages", qkv.dtype)
+            if k_pages.shape[-2:] != (num_kv, head_dim) or v_pages.shape[-2:] != (num_kv, v_dim):
+                raise KernelError(f"qkv_prepare: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)}")
+            num_slots = k_pages.numel() // (num_kv * head_dim)
+        self._check(self.lib.ullm_qkv_prepare(
+            _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), T, num_q, num_kv, head_dim, v_dim, _ptr(conv_w), int(taps),
+            _ptr(conv_state), state_stride, _ptr(cu_q), _ptr(token_req), _ptr(req_slots), state_slots, _ptr(positions),
+            _ptr(inv_freq), int(rotary_dim), _ptr(q_w), _ptr(k_w), int(norm_first), int(norm_last), float(eps),
+            int(vmix_mode), _ptr(vmix_lambda), _ptr(v_first), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages), num_slots,
+            _ptr(q_out), _ptr(self.status), _stream()), f"qkv_prepare (head_dim {head_dim})")
+
+    @_timed("qk_norm_rope_store")
+    def conv_state_update(self, qkv, taps: int, conv_state, cu_q, token_req, req_slots, requests: int):
+        """After `qkv_prepare` of a step: the requests' state rows take the last taps - 1 projected rows."""
+        _need(qkv, "qkv")
+        _need(conv_state, "conv_state", torch.float32)
+        for t_, n_ in ((cu_q, "cu_q"), (token_req, "token_req"), (req_slots, "req_slots")):
+            _need(t_, n_, torch.int32)
+        self._check(self.lib.ullm_conv_state_update(_DT[qkv.dtype], _ptr(qkv), qkv.stride(0), qkv.shape[1], int(taps),
+                                                    _ptr(conv_state), conv_state.stride(0), _ptr(cu_q), _ptr(token_req),
+                                                    _ptr(req_slots), conv_state.shape[0], int(requests), _stream()),
+                    "conv_state_update")
+
+    @_timed("attention")
+    def mix_heads(self, parts, mix, out, num_q, num_kv, v_dim):
+        """out[t, h] = sum_g mix[h, g] * parts[t, g, kv head of h] (parts float32 [T, num_q * num_kv * v_dim])."""
+        _need(parts, "parts", torch.float32)
+        _need(mix, "mix", torch.float32)
+        _need(out, "out")
+        T = out.shape[0]
+        if parts.shape != (T, num_q * num_kv * v_dim) or out.shape[1] != num_q * v_dim or mix.shape != (num_q, num_q):
+            raise KernelError(f"mix_heads: parts {tuple(parts.shape)}, mix {tuple(mix.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_mix_heads(_DT[out.dtype], _ptr(parts), _ptr(mix), _ptr(out), T, num_q, num_kv, v_dim,
+                                            _stream()), "mix_heads")
+
     # -- routed experts -----------------------------------------------------------
     @_timed("moe")
     def moe_route(self, logits, choice, weight, top: int, softmax_scores: bool = False, renormalize: bool = False):
@@ -1060,7 +1252,8 @@ class Kernels:
     @_timed("attention")
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q, num_kv,
                         head_dim, page_size, window, scale, ctx=None, fuse=None, ragged: bool = False,
-                        v_dim: int | None = None, keep_first: int = 0):
+                        v_dim: int | None = None, keep_first: int = 0, softcap: float = 0.0, parts=None,
+                        general: bool = False):
         """Attention of every row of the flat batch over its request's pages.
         `qkv` holds q in its first num_q * head_dim columns.  `fuse` (only after `decode_fusion_applies` said
         yes): q, k and v are as the projection left them, and the kernel norms, rotates and stores them itself;
@@ -1082,6 +1275,23 @@ class Kernels:
         num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
         if keep_first > 0 and not window:
             keep_first = 0
+        if softcap > 0 or parts is not None or general:
+            # capped scores, weights applied to every kv head's values (for `mix_heads`), or a caller that has
+            # prepared q itself and asks for the general kernel
+            if fuse is not None:
+                raise KernelError("paged_attention: q and k were left unprepared, but the general kernel takes this step")
+            if parts is not None:
+                _need(parts, "parts", torch.float32)
+                if parts.shape != (T, num_q * num_kv * v_dim):
+                    raise KernelError(f"paged_attention: parts {tuple(parts.shape)}")
+            self.attention_path = "generic"
+            self._check(self.lib.ullm_paged_attention_generic_ex2(
+                _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), _ptr(token_req), T, num_q, num_kv,
+                head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream(), v_dim,
+                int(keep_first), float(softcap), _ptr(parts)),
+                f"paged_attention (head_dim {head_dim}, values {v_dim}, cap {softcap}, parts {parts is not None})")
+            return
         kept_tc = (keep_first > 0 and v_dim == head_dim and ctx is not None and qkv.dtype == torch.bfloat16
                    and fuse is None and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)
                    and self.lib.ullm_prefill_attention_supported(head_dim, num_q, num_kv))

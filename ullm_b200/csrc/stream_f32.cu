@@ -5,6 +5,9 @@
 //   norm_scale_add    stream[t] += mult * w * a[t] / sqrt(mean(a[t]^2) + eps),       copy[t] = round(stream[t])
 //   rmsnorm_rows_f32  out[r] = round(w * s / sqrt(mean(s^2) + eps)), s = stream[rows[r]]
 //   cast_rows_f32     copy = round(stream)
+//   gated_add_f32     stream[t] += sigmoid(g1[t] + b1) * a[t] (+ sigmoid(g2[t] + b2) * f[t]),       copy[t] = round(stream[t])
+//   side_gate_mul     out[t] = gelu_tanh(s[t]) * table[id[t]][offset .. offset + cols)
+//   softcap_f32       x = cap * tanh(x / cap), in place
 //
 // `copy` is the stream rounded to the engine's dtype, the operand of the next
 // sub-layer's matrix products; with a 32-bit engine it is not needed (null).
@@ -94,6 +97,59 @@ __global__ void cast_rows_f32_kernel(const float* __restrict__ in, T* __restrict
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     out[i] = from_f32<T>(in[i]);
+}
+
+// Two sub-layers that read the same normed rows and are added to the stream together, each through a gate:
+// stream += sigmoid(g1 + b1) * a + sigmoid(g2 + b2) * f.  g1 | g2 are the columns of ONE 32-bit product
+// (row stride `g_stride`); f, g2 and b2 are absent for a layer without the second sub-layer.
+template <typename T>
+__global__ void gated_add_f32_kernel(const T* __restrict__ a, const T* __restrict__ f, const float* __restrict__ g,
+                                     long long g_stride, const float* __restrict__ b1, const float* __restrict__ b2,
+                                     float* __restrict__ stream, T* __restrict__ copy, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long base = (long long)blockIdx.x * cols;
+  const float* gr = g + (long long)blockIdx.x * g_stride;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float y = to_f32(a[base + c]) / (1.f + expf(-(gr[c] + b1[c])));
+    if (f != nullptr) y += to_f32(f[base + c]) / (1.f + expf(-(gr[cols + c] + b2[c])));
+    const float s = stream[base + c] + y;
+    stream[base + c] = s;
+    if (copy != nullptr) copy[base + c] = from_f32<T>(s);
+  }
+}
+
+// out[t][c] = gelu_tanh(s[t][c]) * table[id[t]][offset + c]: a per-token input (a second embedding table, of which
+// a layer reads `cols` columns from `offset` on) gated by a projection of the stream.  An id of -1 is the token
+// the request sampled last, as in the embedding kernels.
+template <typename T>
+__global__ void side_gate_mul_kernel(const T* __restrict__ s, const int* __restrict__ ids, const T* __restrict__ table,
+                                     long long table_stride, int offset, T* __restrict__ out, int cols, int vocab,
+                                     const int* __restrict__ last_tokens, const int* __restrict__ token_req,
+                                     const int* __restrict__ req_slots, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 && last_tokens != nullptr) {
+    const int b = token_req[t];
+    id = b >= 0 ? last_tokens[req_slots[b]] : 0;
+  }
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0) ullm_report(status, ULLM_STATUS_TOKEN_ID, t, id);
+  const T* row = table + (long long)(bad ? 0 : id) * table_stride + offset;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = act_gelu_tanh(to_f32(s[(long long)t * cols + c])) * (bad ? 0.f : to_f32(row[c]));
+    out[(long long)t * cols + c] = from_f32<T>(v);
+  }
+}
+
+__global__ void softcap_f32_kernel(float* __restrict__ x, long long n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float inv = 1.f / cap;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv);
 }
 
 static inline int row_threads(int cols) {
@@ -186,4 +242,57 @@ extern "C" int ullm_cast_rows_f32(int dtype, const float* in, void* out, long lo
   if (dtype == ULLM_DTYPE_F32)
     return ullm_launch_kernel(cast_rows_f32_kernel<float>, grid, block, 0, st, in, (float*)out, n);
   return ULLM_ERR_BAD_DTYPE;
+}
+
+// `f`, `b2` null: one gated sub-layer only (the product then has `cols` columns).
+extern "C" int ullm_gated_add_f32(int dtype, const void* a, const void* f, const float* g, long long g_stride,
+                                  const float* b1, const float* b2, float* stream, void* copy, int rows, int cols,
+                                  void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (rows < 0 || cols <= 0 || g_stride < cols * (f != nullptr ? 2 : 1)) return ULLM_ERR_BAD_SIZE;
+  if ((f != nullptr) != (b2 != nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (rows == 0) return ULLM_OK;
+  const dim3 grid(rows), block(row_threads(cols));
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(gated_add_f32_kernel<float>, grid, block, 0, st, (const float*)a, (const float*)f, g,
+                              g_stride, b1, b2, stream, (float*)copy, cols);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(gated_add_f32_kernel<__nv_bfloat16>, grid, block, 0, st, (const __nv_bfloat16*)a,
+                              (const __nv_bfloat16*)f, g, g_stride, b1, b2, stream, (__nv_bfloat16*)copy, cols);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(gated_add_f32_kernel<__half>, grid, block, 0, st, (const __half*)a, (const __half*)f, g,
+                              g_stride, b1, b2, stream, (__half*)copy, cols);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_side_gate_mul(int dtype, const void* s, const int* ids, const void* table, long long table_stride,
+                                  int offset, void* out, int tokens, int cols, int vocab, const int* last_tokens,
+                                  const int* token_req, const int* req_slots, int* status, void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (tokens < 0 || cols <= 0 || vocab <= 0 || offset < 0 || offset + cols > table_stride) return ULLM_ERR_BAD_SIZE;
+  if (last_tokens != nullptr && (token_req == nullptr || req_slots == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  const dim3 grid(tokens), block(row_threads(cols));
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(side_gate_mul_kernel<float>, grid, block, 0, st, (const float*)s, ids,
+                              (const float*)table, table_stride, offset, (float*)out, cols, vocab, last_tokens,
+                              token_req, req_slots, status);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(side_gate_mul_kernel<__nv_bfloat16>, grid, block, 0, st, (const __nv_bfloat16*)s, ids,
+                              (const __nv_bfloat16*)table, table_stride, offset, (__nv_bfloat16*)out, cols, vocab,
+                              last_tokens, token_req, req_slots, status);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(side_gate_mul_kernel<__half>, grid, block, 0, st, (const __half*)s, ids,
+                              (const __half*)table, table_stride, offset, (__half*)out, cols, vocab, last_tokens,
+                              token_req, req_slots, status);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_softcap_f32(float* x, long long n, float cap, void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (n < 0 || !(cap > 0.f)) return ULLM_ERR_BAD_SIZE;
+  if (n == 0) return ULLM_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return ullm_launch_kernel(softcap_f32_kernel, dim3((int)blocks), dim3(256), 0, st, x, n, cap);
 }

@@ -82,7 +82,7 @@ class ModelRunner:
             torch.set_float32_matmul_precision("highest")
         untie = False
         if load_format == "safetensors" and self.spec.tie_embeddings:
-            untie = files_have(model_dir, self.spec.head_name + "weight")
+            untie = files_have(model_dir, self.spec.head_name + self.spec.head_param)
         self.model = DecoderModel(self.spec, untie_head=untie)
         self.model.allocate(self.device, self.dtype)
         if load_format == "safetensors":

@@ -12,8 +12,10 @@ q_proj / k_proj / v_proj tensors are row ranges of it.
 
 from __future__ import annotations
 
+import torch
+
 from ..csrc import check_attention_sizes, kernels
-from .base import CacheNeed, Mixer, ParamDecl
+from .base import CacheNeed, Mixer, ParamDecl, StateNeed
 from .linear import linear
 from .registry import build_norm, build_position_encoding, register_mixer
 
@@ -42,12 +44,30 @@ class PagedAttention(Mixer):
         keep_first: int = 0,
         own_kv: bool = True,
         names: dict | None = None,
+        conv_taps: int = 0,
+        score_cap: float | None = None,
+        talking_heads: bool = False,
+        value_mix: str | None = None,
+        unit_norm_after_rotation: bool = False,
+        norm_eps: float = 0.0,
     ):
         """`value_dim`: head size of the values and of the output (default: `head_dim`).  `window` with
         `keep_first`: position i sees j <= i if i - j < window or j < keep_first.  `own_kv` False: the mixer has
         no key / value projections (nor a key norm); it reads the cache of the execution the schedule names
         (`ScheduleEntry.cache_of`) with queries, mask and scale of its own.  `names`: the checkpoint's names of
-        q, k, v, o, q_norm, k_norm behind the mixer's prefix (defaults: `q_proj.weight`, ..., `q_norm.`)."""
+        q, k, v, o, q_norm, k_norm behind the mixer's prefix (defaults: `q_proj.weight`, ..., `q_norm.`).
+
+        Further options, all served by the general kernels (csrc/attention_prep.cu, csrc/attention_generic.cu) in
+        prompt and decode steps alike.  `conv_taps` > 0: a causal convolution over time of that many taps on every
+        channel of q, k and v, directly behind the projection (filters `q_conv`, `k_conv`, `v_conv` [channels,
+        taps]); the last taps - 1 projected rows of a request are per-request state.  `score_cap` c: score <-
+        c tanh(score / c) after the scale.  `talking_heads`: the softmax weights are mixed across heads by the
+        matrix `talk` [heads, heads], w'_h = sum_g talk[h, g] w_g, and head h applies w'_h to the values of its
+        own kv head.  `value_mix`: "first": this execution leaves its values of the step's tokens for later ones;
+        "mix": v <- (1 - lambda) v + lambda v_first with the scalar `vmix` (the mixed values are cached); both kinds
+        declare the scalar.  `unit_norm_after_rotation`: q and k are divided by their root mean square over the
+        head (eps `norm_eps`, no weight) behind the rotation.  A position of kind `rope_computed` (angles computed
+        in the kernel, optional frequency scaling) also takes this path."""
         super().__init__()
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
@@ -63,8 +83,23 @@ class PagedAttention(Mixer):
         self.own_kv = bool(own_kv)
         if self.keep_first < 0 or self.value_dim <= 0:
             raise ValueError("keep_first must not be negative and value_dim must be positive")
+        self.conv_taps = int(conv_taps)
+        self.score_cap = float(score_cap) if score_cap else None
+        self.talking_heads = bool(talking_heads)
+        self.value_mix = value_mix
+        self.unit_norm_after_rotation = bool(unit_norm_after_rotation)
+        self.norm_eps = float(norm_eps)
+        if self.conv_taps < 0 or self.conv_taps > 8:
+            raise ValueError(f"conv_taps={conv_taps}: the convolution kernel takes 1 to 8 taps (0: none)")
+        if self.score_cap is not None and self.score_cap <= 0:
+            raise ValueError("score_cap must be positive")
+        if value_mix not in (None, "first", "mix"):
+            raise ValueError(f"value_mix={value_mix!r}: None, 'first' or 'mix'")
+        if not self.own_kv and (self.conv_taps or value_mix):
+            raise ValueError("a mixer without key / value projections has no values to convolve or to mix")
         n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_bias="q_proj.bias",
-                 k_bias="k_proj.bias", v_bias="v_proj.bias", q_norm="q_norm.", k_norm="k_norm.")
+                 k_bias="k_proj.bias", v_bias="v_proj.bias", q_norm="q_norm.", k_norm="k_norm.",
+                 q_conv="q_proj.conv", k_conv="k_proj.conv", v_conv="v_proj.conv", talk="talk", vmix="vmix")
         n.update(names or {})
         self.names = n
         self.q_size = num_heads * head_dim
@@ -74,6 +109,10 @@ class PagedAttention(Mixer):
         self.q_norm = build_norm(qk_norm) if qk_norm is not None else None
         self.k_norm = build_norm(qk_norm) if (qk_norm is not None and self.own_kv) else None
         self.position = build_position_encoding(position) if position is not None else None
+        self.general = bool(self.conv_taps or self.score_cap or self.talking_heads or value_mix
+                            or self.unit_norm_after_rotation or getattr(self.position, "computed", False))
+        if self.general and self.position is not None and not getattr(self.position, "computed", False):
+            raise ValueError("these attention options take a position encoding of kind 'rope_computed' (or none)")
         check_attention_sizes(num_heads, num_kv_heads, head_dim, self.position.rotary_dim if self.position else 0)
 
     # -- parameters -------------------------------------------------------
@@ -88,6 +127,14 @@ class PagedAttention(Mixer):
             if self.own_kv:
                 d[n["k_bias"]] = ParamDecl((self.kv_size,), "bias")
                 d[n["v_bias"]] = ParamDecl((self.v_size,), "bias")
+        if self.conv_taps:
+            d[n["q_conv"]] = ParamDecl((self.q_size, self.conv_taps))
+            d[n["k_conv"]] = ParamDecl((self.kv_size, self.conv_taps))
+            d[n["v_conv"]] = ParamDecl((self.v_size, self.conv_taps))
+        if self.talking_heads:
+            d[n["talk"]] = ParamDecl((self.num_heads, self.num_heads), "bias32")
+        if self.value_mix:
+            d[n["vmix"]] = ParamDecl((), "bias32")
         return d
 
     def subparts(self):
@@ -114,6 +161,17 @@ class PagedAttention(Mixer):
             if self.own_kv:
                 self.tensors[n["k_bias"]] = self.b_qkv[q:q + kv]
                 self.tensors[n["v_bias"]] = self.b_qkv[q + kv:]
+        self.w_conv = None
+        if self.conv_taps:
+            # the three filters one after the other, as the projection's rows are
+            self.w_conv = make("qkv_proj.conv", ParamDecl((rows, self.conv_taps)))
+            self.tensors[n["q_conv"]] = self.w_conv[:q]
+            self.tensors[n["k_conv"]] = self.w_conv[q:q + kv]
+            self.tensors[n["v_conv"]] = self.w_conv[q + kv:]
+        if self.talking_heads:
+            self.tensors[n["talk"]] = make(n["talk"], ParamDecl((self.num_heads, self.num_heads), "bias32"))
+        if self.value_mix:
+            self.tensors[n["vmix"]] = make(n["vmix"], ParamDecl((), "bias32"))
         if self.position is not None:
             self.position.build_tables(self.w_qkv.device)
 
@@ -122,9 +180,21 @@ class PagedAttention(Mixer):
         return CacheNeed(self.num_kv_heads, self.head_dim, self.window,
                          None if self.value_dim == self.head_dim else self.value_dim, self.keep_first if self.window else 0)
 
+    def state_need(self):
+        """The convolution's memory: the last taps - 1 projected rows (q | k | v) of the request, 32-bit."""
+        if self.conv_taps > 1:
+            return StateNeed(((self.conv_taps - 1) * (self.q_size + self.kv_size + self.v_size),), torch.float32)
+        return None
+
     def activation_elems(self):
-        # qkv, the attention's output, the projected output
-        return self.q_size + self.kv_size + self.v_size + self.o_size + self.hidden_size
+        # qkv, the attention's output, the projected output; on the general path also the prepared queries, the
+        # first layer's values, and with mixed heads every head's weights on every kv head's values in 32-bit
+        n = self.q_size + self.kv_size + self.v_size + self.o_size + self.hidden_size
+        if self.general:
+            n += self.q_size + self.v_size
+            if self.talking_heads:
+                n += 2 * self.num_kv_heads * self.o_size
+        return n
 
     # -- which kernels a decode step takes ---------------------------------
     def graph_key(self, ctx):
@@ -141,10 +211,71 @@ class PagedAttention(Mixer):
         return self.tensors[self.names["o"]], None
 
     def takes_input_norm(self):
-        return True
+        return not self.general
+
+    # -- the general path ----------------------------------------------------
+    def _forward_general(self, x, ctx, cache, project_output: bool):
+        """Projection, then csrc/attention_prep.cu (convolution, rotation, norms, value mixing, cache stores), the
+        general attention kernel (cap, window, kept tokens), and the mixing of heads if there is any."""
+        K = kernels()
+        T = x.shape[0]
+        ws = ctx.workspace
+        if not self.own_kv:
+            raise NotImplementedError("borrowed keys and values beside these attention options")
+        qkv = ws.tokens("attn.qkv", T, self.w_qkv.shape[0], x.dtype)
+        linear(x, self.w_qkv, qkv, self.b_qkv)
+        g = cache.group
+        q = ws.tokens("attn.q", T, self.q_size, x.dtype)
+        tables = self.position.tables() if self.position is not None else {}
+        rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        v_first, mode = None, 0
+        if self.value_mix == "first":
+            v_first = ws.tokens("attn.v_first", T, self.v_size, x.dtype)
+            ctx.shared["attn.v_first"] = v_first
+            mode = 1
+        elif self.value_mix == "mix":
+            v_first = ctx.shared.get("attn.v_first")
+            if v_first is None or v_first.shape != (T, self.v_size):
+                raise RuntimeError("value mixing: no earlier execution of this step left values of this width")
+            mode = 2
+        state = cache.state if self.conv_taps > 1 else None
+        if self.conv_taps > 1 and state is None:
+            raise RuntimeError("the attention's convolution was given no state rows")
+        K.qkv_prepare(
+            qkv, q, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, ctx.positions,
+            g.slot_mapping if cache.writes else None, cache.k_pages, cache.v_pages,
+            conv_w=self.w_conv, taps=self.conv_taps, conv_state=state, cu_q=ctx.cu_q, token_req=ctx.token_req,
+            req_slots=ctx.req_slots, inv_freq=tables.get("inv_freq"), rotary_dim=rotary_dim,
+            q_w=self.q_norm.weight if self.q_norm is not None else None,
+            k_w=self.k_norm.weight if self.k_norm is not None else None, norm_first=self.q_norm is not None,
+            norm_last=self.unit_norm_after_rotation,
+            eps=self.q_norm.eps if self.q_norm is not None else self.norm_eps,
+            vmix_mode=mode, vmix_lambda=self.tensors[self.names["vmix"]] if mode == 2 else None, v_first=v_first)
+        if state is not None:
+            K.conv_state_update(qkv, self.conv_taps, state, ctx.cu_q, ctx.token_req, ctx.req_slots, ctx.num_requests)
+        attn = ws.tokens("attn.out", T, self.o_size, x.dtype)
+        parts = None
+        if self.talking_heads:
+            parts = ws.tokens("attn.parts", T, self.num_heads * self.num_kv_heads * self.value_dim, torch.float32)
+        K.paged_attention(
+            q, attn, cache.k_pages, cache.v_pages, g.block_table, g.req_slots, ctx.cu_q, g.kv_len, ctx.token_req,
+            self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, self.window or 0, self.scale, ctx,
+            v_dim=self.value_dim, keep_first=self.keep_first if self.window else 0, softcap=self.score_cap or 0.0,
+            parts=parts, general=True)
+        if parts is not None:
+            K.mix_heads(parts, self.tensors[self.names["talk"]], attn, self.num_heads, self.num_kv_heads, self.value_dim)
+        if not project_output:
+            return attn
+        out = ws.tokens("mixer.out", T, self.hidden_size, x.dtype)
+        linear(attn, self.tensors[self.names["o"]], out)
+        return out
 
     # -- one step ---------------------------------------------------------
     def forward(self, x, ctx, cache, project_output: bool = True, input_norm=None):
+        if self.general:
+            if input_norm is not None:
+                raise RuntimeError("a folded norm was handed to an attention that does not take one")
+            return self._forward_general(x, ctx, cache, project_output)
         K = kernels()
         T = x.shape[0]
         ragged = self._ragged(ctx)

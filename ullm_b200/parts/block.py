@@ -10,7 +10,8 @@ from __future__ import annotations
 import torch
 
 from ..csrc import kernels
-from .base import Block
+from .base import Block, ParamDecl
+from .linear import linear
 from .registry import register_block
 
 
@@ -207,4 +208,114 @@ class OutputNormResidualBlock(Block):
             y = self.feed_forward.forward(h, ctx)
             self.feed_forward_norm.scale_add(y, stream, self.residual_mult, copy)
         ctx.stream_operand = h
+        return None, stream
+
+
+@register_block("parallel_gated")
+class ParallelGatedBlock(Block):
+    """Mixer and feed-forward read the same normed stream and are added to it together:
+
+        h = norm(x);   x <- x + (g1 * mixer(h) + g2 * feed_forward(h))
+
+    with g_i = sigmoid(R_i h + b_i) element by element when `gated` (else 1), and, when `side_dim` > 0, a
+    per-layer token input behind it: with e the layer's share (`side_index`) of the model's token side table,
+
+        y = P (gelu_tanh(G x) * e);   x <- x + n * y / sqrt(mean(y^2) + eps)
+
+    The stream is 32-bit whatever the engine's dtype (the model is built with `stream_dtype="float32"`); the gates'
+    projections are ONE product with a 32-bit result, and sigmoids, sums and norms are 32-bit.  A layer may have no
+    feed-forward (then no second gate either).  `feed_forward_norm` is unused: there is one norm."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, names=None, gated: bool = True,
+                 side_dim: int = 0, side_index: int = 0, eps: float = 1e-6):
+        super().__init__()
+        if feed_forward_norm is not None:
+            raise ValueError("a parallel block has one norm (feed_forward_norm must be None)")
+        if not gated:
+            raise ValueError("the parallel block without gates is not built (gated=True)")
+        self.mixer, self.feed_forward, self.mixer_norm = mixer, feed_forward, mixer_norm
+        self.gated, self.side_dim, self.side_index, self.eps = bool(gated), int(side_dim), int(side_index), float(eps)
+        self.hidden_size = mixer_norm.size
+        n = dict(mixer="mixer.", feed_forward="feed_forward.", mixer_norm="norm.", gate1="gate1.weight",
+                 gate1_bias="gate1.bias", gate2="gate2.weight", gate2_bias="gate2.bias", side_gate="side.gate",
+                 side_proj="side.proj", side_norm="side.norm")
+        n.update(names or {})
+        self.names = n
+
+    def subparts(self):
+        s = {self.names["mixer_norm"]: self.mixer_norm, self.names["mixer"]: self.mixer}
+        if self.feed_forward is not None:
+            s[self.names["feed_forward"]] = self.feed_forward
+        return s
+
+    def param_decls(self):
+        W, n, d = self.hidden_size, self.names, {}
+        if self.gated:
+            d[n["gate1"]] = ParamDecl((W, W))
+            d[n["gate1_bias"]] = ParamDecl((W,), "bias32")
+            if self.feed_forward is not None:
+                d[n["gate2"]] = ParamDecl((W, W))
+                d[n["gate2_bias"]] = ParamDecl((W,), "bias32")
+        if self.side_dim:
+            d[n["side_gate"]] = ParamDecl((self.side_dim, W))
+            d[n["side_proj"]] = ParamDecl((W, self.side_dim))
+            d[n["side_norm"]] = ParamDecl((W,), "norm")
+        return d
+
+    def materialize(self, make):
+        W, n = self.hidden_size, self.names
+        self.w_gates = None
+        if self.gated:
+            two = self.feed_forward is not None
+            # the two gates' projections as one matrix with rows gate1 | gate2
+            self.w_gates = make("gates.weight", ParamDecl(((2 if two else 1) * W, W)))
+            self.tensors[n["gate1"]] = self.w_gates[:W]
+            self.tensors[n["gate1_bias"]] = make(n["gate1_bias"], ParamDecl((W,), "bias32"))
+            if two:
+                self.tensors[n["gate2"]] = self.w_gates[W:]
+                self.tensors[n["gate2_bias"]] = make(n["gate2_bias"], ParamDecl((W,), "bias32"))
+        if self.side_dim:
+            self.tensors[n["side_gate"]] = make(n["side_gate"], ParamDecl((self.side_dim, W)))
+            self.tensors[n["side_proj"]] = make(n["side_proj"], ParamDecl((W, self.side_dim)))
+            self.tensors[n["side_norm"]] = make(n["side_norm"], ParamDecl((W,), "norm"))
+
+    def activation_elems(self):
+        W = self.hidden_size
+        ff = self.feed_forward.activation_elems() if self.feed_forward is not None else 0
+        # the normed rows, the stream's copy, both sub-layers at once, the gates in 32-bit, the side input
+        return 2 * W + self.mixer.activation_elems() + ff + 4 * W + 2 * self.side_dim + W
+
+    def forward(self, x, residual, ctx, cache):
+        """The stream arrives as `x` (first block, residual None) or as `residual` (x None); returns (None, stream)."""
+        K = kernels()
+        stream = residual if residual is not None else x
+        if stream.dtype != torch.float32:
+            raise RuntimeError("this block takes a 32-bit residual stream (ModelSpec.stream_dtype='float32')")
+        T, W = stream.shape
+        n, ws = self.names, ctx.workspace
+        dt = self.mixer.operand_dtype()
+        h = ws.tokens("block.normed", T, W, dt)
+        self.mixer_norm.forward_rows(stream, None, h)
+        a = self.mixer.forward(h, ctx, cache)
+        f = self.feed_forward.forward(h, ctx) if self.feed_forward is not None else None
+        copy = ws.tokens("model.stream_copy", T, W, dt) if (self.side_dim and dt != torch.float32) else None
+        gates = ws.tokens("block.gates", T, self.w_gates.shape[0], torch.float32)
+        K.linear_f32_out(h, self.w_gates, gates)
+        K.gated_add_f32(a, f, gates, self.tensors[n["gate1_bias"]],
+                        self.tensors[n["gate2_bias"]] if f is not None else None, stream, copy)
+        if self.side_dim:
+            side = ctx.token_side
+            if side is None or side.dim != self.side_dim or not 0 <= self.side_index < side.shares:
+                raise RuntimeError("this block's per-layer token input does not fit the model's token side table")
+            operand = copy if copy is not None else stream
+            s = ws.tokens("block.side_gate", T, self.side_dim, dt)
+            linear(operand, self.tensors[n["side_gate"]], s)
+            g = ws.tokens("block.side_in", T, self.side_dim, dt)
+            last = ctx.last_tokens
+            K.side_gate_mul(s, ctx.token_ids, side.table, self.side_index * self.side_dim, g, last,
+                            ctx.token_req if last is not None else None, ctx.req_slots if last is not None else None)
+            y = ws.tokens("block.side_out", T, W, dt)
+            linear(g, self.tensors[n["side_proj"]], y)
+            K.norm_scale_add(y, stream, self.tensors[n["side_norm"]], self.eps, 1.0, None)
+        ctx.stream_operand = None
         return None, stream

@@ -56,12 +56,35 @@ class TokenEmbedding(Part):
         return out
 
 
-class OutputHead(Part):
-    """logits = h W^T in 32-bit output.  `tied_to`, when set, is the embedding
-    part whose table is read and no tensor of its own is declared."""
+class TokenSideTable(Part):
+    """A second table indexed by token id, [vocab, shares * dim]: share i (columns i * dim .. (i + 1) * dim) is what
+    layer i reads of its tokens' rows.  The model puts the part into the step's context (`ctx.token_side`); a
+    block that takes a per-layer token input reads `table` with its own share's offset."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None, param: str = "weight"):
+    def __init__(self, vocab_size: int, dim: int, shares: int, param: str = ""):
         super().__init__()
+        if min(vocab_size, dim, shares) <= 0:
+            raise ValueError("a token side table needs positive sizes")
+        self.vocab_size, self.dim, self.shares, self.param = vocab_size, dim, shares, param
+
+    def param_decls(self):
+        return {self.param: ParamDecl((self.vocab_size, self.shares * self.dim))}
+
+    @property
+    def table(self):
+        return self.tensors[self.param]
+
+
+class OutputHead(Part):
+    """logits = h W^T in 32-bit output, then optionally capped: cap * tanh(logits / cap).  `tied_to`, when set, is
+    the embedding part whose table is read and no tensor of its own is declared."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: TokenEmbedding | None = None, param: str = "weight",
+                 softcap: float | None = None):
+        super().__init__()
+        if softcap is not None and not softcap > 0:
+            raise ValueError("a logit cap must be positive")
+        self.softcap = softcap
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
@@ -77,4 +100,6 @@ class OutputHead(Part):
 
     def forward(self, h, out_f32):
         kernels().linear_f32_out(h, self.weight(), out_f32)
+        if self.softcap is not None:
+            kernels().softcap_f32(out_f32, self.softcap)
         return out_f32

@@ -13,7 +13,7 @@ import torch
 from ..config.specs import ModelSpec
 from ..csrc import kernels
 from .base import Part
-from .embedding import OutputHead, TokenEmbedding
+from .embedding import OutputHead, TokenEmbedding, TokenSideTable
 from .registry import build_block, build_norm, build_position_encoding
 
 
@@ -37,7 +37,11 @@ class DecoderModel(Part):
         self.blocks = [build_block(ls) for ls in spec.layers]
         self.final_norm = build_norm(spec.final_norm)
         tied = spec.tie_embeddings and not untie_head
-        self.head = OutputHead(spec.vocab_size, spec.hidden_size, self.embedding if tied else None, spec.head_param)
+        self.head = OutputHead(spec.vocab_size, spec.hidden_size, self.embedding if tied else None, spec.head_param,
+                               softcap=spec.logit_softcap)
+        self.token_side = None
+        if spec.token_side is not None:
+            self.token_side = TokenSideTable(spec.vocab_size, spec.token_side.dim, spec.token_side.shares)
         self.schedule = list(spec.schedule)
         # one mixer of each group answers `graph_key` for all of its kind
         seen: dict = {}
@@ -54,6 +58,8 @@ class DecoderModel(Part):
             s[self.spec.layer_name.format(i)] = b
         s[self.spec.final_norm_name] = self.final_norm
         s[self.spec.head_name] = self.head
+        if self.token_side is not None:
+            s[self.spec.token_side.name] = self.token_side
         return s
 
     # -- what the cache manager needs to know ------------------------------
@@ -88,6 +94,8 @@ class DecoderModel(Part):
         (or None) and the residual stream, before the final norm."""
         T = ctx.num_tokens
         ctx.stream_operand = None
+        ctx.token_side = self.token_side
+        ctx.shared = {}  # what one execution leaves for later ones of the same step (first-layer values, say)
         if self.stream_f32:
             # the stream is 32-bit; its copy rounded to the engine's dtype is the first sub-layer's operand
             x = ctx.workspace.tokens("model.stream", T, self.spec.hidden_size, torch.float32)
