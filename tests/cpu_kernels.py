@@ -127,7 +127,8 @@ class CpuKernels:
         qkv.copy_(x.view(T, -1).to(qkv.dtype))
 
     def paged_attention(self, qkv, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req,
-                        num_q, num_kv, D, page_size, window, scale, ctx=None, ragged=False, v_dim=None, keep_first=0):
+                        num_q, num_kv, D, page_size, window, scale, ctx=None, ragged=False, v_dim=None, keep_first=0,
+                        softcap=0.0, parts=None, general=False):
         self._count("paged_attention")
         T = out.shape[0]
         Dv = D if v_dim is None else v_dim
@@ -136,6 +137,8 @@ class CpuKernels:
         q = qkv[:T, : num_q * D].float().reshape(T, num_q, D)
         group = num_q // num_kv
         o = torch.zeros(T, num_q, Dv)
+        if parts is not None:
+            parts.zero_()
         for t in range(T):
             r = int(token_req[t])
             if r < 0:
@@ -153,9 +156,141 @@ class CpuKernels:
             for h in range(num_q):
                 kh = h // group
                 s = (kf[slots, kh] @ q[t, h]) * scale
+                if softcap > 0:
+                    s = softcap * torch.tanh(s / softcap)
                 p = torch.softmax(s, 0)
                 o[t, h] = p @ vf[slots, kh]
-        out.copy_(o.reshape(T, num_q * Dv).to(out.dtype))
+                if parts is not None:
+                    parts.view(T, num_q, num_kv, Dv)[t, h] = torch.einsum("j,jcd->cd", p, vf[slots])
+        if parts is None:
+            out.copy_(o.reshape(T, num_q * Dv).to(out.dtype))
+
+    def mix_heads(self, parts, mix, out, num_q, num_kv, v_dim):
+        T = out.shape[0]
+        p = parts.view(T, num_q, num_kv, v_dim)
+        own = p[:, :, torch.arange(num_q) // (num_q // num_kv)]  # [T, g, h, dv]: head g's weights on head h's values
+        out.copy_(torch.einsum("hg,tghd->thd", mix.float(), own).reshape(T, -1).to(out.dtype))
+
+    def qkv_prepare(self, qkv, q_out, num_q, num_kv, head_dim, v_dim, positions, slot_mapping, k_pages, v_pages, *,
+                    conv_w=None, taps=0, conv_state=None, cu_q=None, token_req=None, req_slots=None, inv_freq=None,
+                    rotary_dim=0, q_w=None, k_w=None, norm_first=False, norm_last=False, eps=0.0, vmix_mode=0,
+                    vmix_lambda=None, v_first=None):
+        self._count("qkv_prepare")
+        T, W = qkv.shape
+        x = qkv.float().clone()
+        if conv_w is not None:
+            y = torch.zeros_like(x)
+            for t in range(T):
+                r = int(token_req[t])
+                if r < 0:
+                    y[t] = x[t]
+                    continue
+                t0 = int(cu_q[r])
+                for j in range(taps):
+                    row = t - (taps - 1 - j)
+                    if row >= t0:
+                        u = x[row]
+                    else:
+                        u = conv_state[int(req_slots[r])].view(-1, W)[taps - 1 - (t0 - row)]
+                    y[t] += conv_w[:, j].float() * u
+            x = y
+        qs, ks = num_q * head_dim, num_kv * head_dim
+        q, k, v = x[:, :qs].reshape(T, num_q, head_dim), x[:, qs:qs + ks].reshape(T, num_kv, head_dim), x[:, qs + ks:]
+
+        def unit(u, w):
+            u = u / torch.sqrt(u.pow(2).mean(-1, keepdim=True) + eps)
+            return u * w if w is not None else u
+
+        if norm_first:
+            q, k = unit(q, q_w), unit(k, k_w)
+        if rotary_dim > 0:
+            half = rotary_dim // 2
+            ang = positions[:T].float()[:, None] * inv_freq[None, :half]
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+            def rot(u):
+                a, b = u[..., :half], u[..., half:rotary_dim]
+                return torch.cat((a * cos - b * sin, b * cos + a * sin, u[..., rotary_dim:]), -1)
+
+            q, k = rot(q), rot(k)
+        if norm_last:
+            q, k = unit(q, None), unit(k, None)
+        if vmix_mode == 2:
+            lam = float(vmix_lambda)
+            v = (1.0 - lam) * v + lam * v_first.float()
+        v = v.to(qkv.dtype)
+        if vmix_mode == 1:
+            v_first.copy_(v)
+        q_out.copy_(q.reshape(T, -1).to(q_out.dtype))
+        if slot_mapping is not None:
+            kf, vf = k_pages.view(-1, num_kv, head_dim), v_pages.view(-1, num_kv, v_dim)
+            for t in range(T):
+                s = int(slot_mapping[t])
+                if s >= 0:
+                    kf[s] = k[t].to(kf.dtype)
+                    vf[s] = v[t].view(num_kv, v_dim)
+
+    def conv_state_update(self, qkv, taps, conv_state, cu_q, token_req, req_slots, requests):
+        W = qkv.shape[1]
+        for r in range(requests):
+            t0, t1 = int(cu_q[r]), int(cu_q[r + 1])
+            if t1 <= t0 or int(token_req[t0]) < 0:
+                continue
+            st = conv_state[int(req_slots[r])].view(-1, W)[: taps - 1]
+            rows = torch.cat((st, qkv[t0:t1].float()))[-(taps - 1):]
+            st.copy_(rows)
+
+    def gla_recurrence(self, qkv, q_off, k_off, v_off, z, z_bias, inv_tau, q_scale, state, cu_q, req_slots, token_req,
+                       out, requests, heads, dim, vdim):
+        self._count("gla")
+        x = qkv.float()
+        for r in range(requests):
+            t0, t1 = int(cu_q[r]), int(cu_q[r + 1])
+            if t1 <= t0:
+                continue
+            if int(token_req[t0]) < 0:
+                out[t0:t1] = 0
+                continue
+            S = state[int(req_slots[r])][: heads * vdim * dim].view(heads, vdim, dim)
+            for t in range(t0, t1):
+                q = x[t, q_off:q_off + heads * dim].view(heads, dim) * q_scale
+                k = x[t, k_off:k_off + heads * dim].view(heads, dim)
+                v = x[t, v_off:v_off + heads * vdim].view(heads, vdim)
+                zz = z[t] + (z_bias if z_bias is not None else 0)
+                a = torch.exp(torch.nn.functional.logsigmoid(zz) * inv_tau).view(heads, dim)
+                S.mul_(a[:, None, :]).add_(v[:, :, None] * k[:, None, :])
+                out[t] = torch.einsum("hvd,hd->hv", S, q).reshape(-1)
+
+    def head_norm_gate(self, o, g, weight, eps, out, heads, vdim, silu=False):
+        T = o.shape[0]
+        x = o.view(T, heads, vdim)
+        x = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        w = weight.view(heads, vdim) if weight.numel() == heads * vdim else weight.view(1, vdim)
+        gf = g.float()
+        gate = torch.nn.functional.silu(gf) if silu else torch.sigmoid(gf)
+        out.copy_(((x * w).reshape(T, -1) * gate).to(out.dtype))
+
+    def gated_add_f32(self, a, f, gates, b1, b2, stream, copy=None):
+        self._count("add_rmsnorm")
+        W = a.shape[1]
+        stream += torch.sigmoid(gates[:, :W] + b1) * a.float()
+        if f is not None:
+            stream += torch.sigmoid(gates[:, W:] + b2) * f.float()
+        if copy is not None:
+            copy.copy_(stream.to(copy.dtype))
+
+    def side_gate_mul(self, s, ids, table, offset, out, last_tokens=None, token_req=None, req_slots=None):
+        T, C = s.shape
+        idx = ids[:T].long().clone()
+        if last_tokens is not None:
+            for t in (idx < 0).nonzero().flatten().tolist():
+                b = int(token_req[t])
+                idx[t] = int(last_tokens[int(req_slots[b])]) if b >= 0 else 0
+        e = table[idx][:, offset:offset + C].float()
+        out.copy_((torch.nn.functional.gelu(s.float(), approximate="tanh") * e).to(out.dtype))
+
+    def softcap_f32(self, x, cap):
+        x.copy_(cap * torch.tanh(x / cap))
 
     # -- a 32-bit residual stream, matrix memory, routed experts -----------------------------
     def embed_scaled(self, ids, table, stream, copy=None, scale=1.0, inv_freq=None, positions=None, last_tokens=None,

@@ -236,3 +236,70 @@ def forward(config, w, tokens, return_layers=False):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+# -- tensor names, shapes and random weights of a configuration ---------------------------------------------
+def tensor_shapes(config, decay_rank=5):
+    """{name: shape} of every tensor a model of this configuration has."""
+    W, V = config["width"], config["vocab"]
+    out = {"embed": (V, W), "final.norm": (W,)}
+    side = config.get("token_side")
+    if side:
+        out["side.embed"] = (V, len(config["layers"]) * side["dim"])
+    for i, L in enumerate(config["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out[p + "norm1"] = (W,)
+        out[p + "rg1"], out[p + "rg1.b"] = (W, W), (W,)
+        if L["type"] == "gla":
+            N, d, dv = m["heads"], m["dim"], m["vdim"]
+            r = m.get("decay_rank", decay_rank)
+            out.update({p + "mix.q": (N * d, W), p + "mix.k": (N * d, W), p + "mix.v": (N * dv, W),
+                        p + "mix.g": (N * dv, W), p + "mix.o": (W, N * dv), p + "mix.norm": (dv,),
+                        p + "mix.a1": (r, W), p + "mix.a2": (N * d, r), p + "mix.a2.b": (N * d,)})
+        else:
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            out.update({p + "mix.q": (H * d, W), p + "mix.k": (G * d, W), p + "mix.v": (G * dv, W),
+                        p + "mix.o": (W, H * dv)})
+            if m.get("conv"):
+                out.update({p + "mix.q.conv": (H * d, m["conv"]), p + "mix.k.conv": (G * d, m["conv"]),
+                            p + "mix.v.conv": (G * dv, m["conv"])})
+            if L["type"] == "attention":
+                out[p + "mix.talk"] = (H, H)
+            if m.get("v_mix"):
+                out[p + "mix.vmix"] = ()
+        if L.get("mlp") is not None:
+            F = L["mlp"]["ff"]
+            out.update({p + "mlp.gate": (F, W), p + "mlp.up": (F, W), p + "mlp.down": (W, F),
+                        p + "rg2": (W, W), p + "rg2.b": (W,)})
+        if side:
+            out.update({p + "side.gate": (side["dim"], W), p + "side.proj": (W, side["dim"]), p + "side.norm": (W,)})
+    return out
+
+
+def random_weights(config, seed=0, decay_rank=5):
+    """32-bit tensors sized so that every mechanism matters: linear maps keep unit variance, norm weights scatter
+    around one, the head mixer around the identity, decays near (but not at) one."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tensor_shapes(config, decay_rank).items():
+        t = torch.randn(shape, generator=g)
+        if name.endswith(("norm1", ".norm", "final.norm")):
+            t = 1.0 + 0.2 * t
+        elif name.endswith("talk"):
+            t = torch.eye(shape[0]) + 0.3 * t
+        elif name.endswith("vmix"):
+            t = 0.3 + 0.1 * t
+        elif name.endswith("a2.b"):
+            t = 2.0 + t
+        elif name.endswith(".b"):
+            t = 0.5 * t
+        elif name.endswith(".conv"):
+            t = 0.6 * t
+        elif name == "embed":
+            t = 3.0 * t / math.sqrt(shape[1])  # (logits of a few units: a cap of that order bends but does not flatten them)
+        elif name == "side.embed":
+            t = t
+        elif len(shape) == 2:
+            t = t / math.sqrt(shape[1])
+        w[name] = t
+    return w

@@ -56,8 +56,8 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, long long row_stri
   if (conv_w != nullptr && r >= 0) {
     const int t0 = cu_q[r];
     const int slot = req_slots[r];
-    const bool slot_ok = slot >= 0 && slot < num_state_slots;
-    if (!slot_ok && lane == 0) ullm_report(status, ULLM_STATUS_SLOT, t, slot);
+    const bool slot_ok = taps > 1 && slot >= 0 && slot < num_state_slots;  // (one tap: no memory, no state row)
+    if (taps > 1 && !slot_ok && lane == 0) ullm_report(status, ULLM_STATUS_SLOT, t, slot);
     const float* st = conv_state + (long long)(slot_ok ? slot : 0) * state_stride;
     const int row_width = q_size + k_size + num_kv * v_dim;
     for (int e = lane; e < dim; e += 32) {
