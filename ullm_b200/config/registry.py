@@ -64,11 +64,15 @@ def load_model_spec(model_dir_or_dict) -> tuple[Any, ModelSpec]:
     if arch.reads_shapes:
         shapes = None
         if not isinstance(model_dir_or_dict, dict):
+            import glob
+
             from ..weights.safetensors_io import open_model_files
 
-            files = open_model_files(model_dir_or_dict)
+            # (a folder without weight files, as for random weights: the sizes that shapes give take their defaults)
+            has = bool(glob.glob(os.path.join(model_dir_or_dict, "*.safetensors")))
+            files = open_model_files(model_dir_or_dict) if has else []
             try:
-                shapes = {n: tuple(f.shape(n)) for f in files for n in f.names()}
+                shapes = {n: tuple(f.shape(n)) for f in files for n in f.names()} if has else None
             finally:
                 for f in files:
                     f.close()

@@ -46,6 +46,8 @@ struct DecFuse {
   int max_positions;
   float eps;
   int keep_first;  // with a window: the positions below it stay visible (0: none)
+  float cap_pre;   // capped scores, s <- cap * tanh(s * scale / cap): scale / cap here (0: no cap) ...
+  float cap_post;  // ... and cap * log2(e) here
 };
 
 // 2^x by the hardware's unit alone (exp2f adds a range fix-up around the same instruction)
@@ -53,6 +55,11 @@ __device__ __forceinline__ float dec_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// tanh by one exponential and one division of the hardware's units: 1 - 2 / (e^(2x) + 1)
+__device__ __forceinline__ float dec_tanh(float x) {
+  return 1.f - __fdividef(2.f, dec_ex2(x * 2.8853900817779268f) + 1.f);
 }
 
 // CL: the splits of a (request, kv head) pair are the blocks of one thread-block cluster (at most 8) and merge
@@ -337,7 +344,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = base + t * 8 + (lane & 3) * 2 + (e & 1);
-        const float v = key < w_end ? sc[t][e] * scale_log2 : -INFINITY;
+        const float raw = fu.cap_pre > 0.f ? dec_tanh(sc[t][e] * fu.cap_pre) * fu.cap_post : sc[t][e] * scale_log2;
+        const float v = key < w_end ? raw : -INFINITY;
         sc[t][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -642,6 +650,23 @@ extern "C" int ullm_decode_attention_kept(const void* q, long long q_row_stride,
   if (keep_first < 0) return ULLM_ERR_BAD_SIZE;
   DecFuse fu = {};
   fu.keep_first = window > 0 ? keep_first : 0;
+  return decode_attention_impl(q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, scratch,
+                               batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits, num_pages, status,
+                               stream, fu);
+}
+
+// With capped scores, s <- softcap * tanh(s * scale / softcap), beside a window with kept first positions.
+extern "C" int ullm_decode_attention_capped(const void* q, long long q_row_stride, const void* k_cache,
+                                            const void* v_cache, const int* block_table, int max_pages,
+                                            const int* req_slots, const int* kv_len, void* out, float* scratch,
+                                            int batch, int num_q, int num_kv, int head_dim, int page_size, int window,
+                                            float scale, int num_splits, long long num_pages, int* status,
+                                            void* stream, int keep_first, float softcap) {
+  if (keep_first < 0 || !(softcap > 0.f)) return ULLM_ERR_BAD_SIZE;
+  DecFuse fu = {};
+  fu.keep_first = window > 0 ? keep_first : 0;
+  fu.cap_pre = scale / softcap;
+  fu.cap_post = softcap * 1.4426950408889634f;
   return decode_attention_impl(q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, scratch,
                                batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits, num_pages, status,
                                stream, fu);

@@ -71,14 +71,24 @@ struct PrefillSmem {
   static constexpr int BYTES = Q_BYTES + 2 * 2 * TILE_BYTES + SLOT_BYTES;
 };
 
-template <int D>
+// tanh by one exponential and one division of the hardware's units: 1 - 2 / (e^(2x) + 1); absolute error of a
+// few 2^-24 (the scores it caps are of order one to a hundred), exact limits at +-infinity
+__device__ __forceinline__ float pre_tanh(float x) {
+  return 1.f - __fdividef(2.f, pre_ex2(x * 2.8853900817779268f) + 1.f);
+}
+
+// CAP: scores are capped, s <- cap * tanh(s * scale / cap) (`cap_pre` = scale / cap, `scale_log2` = cap * log2 e).
+// PARTS: a block serves a (key head, VALUE head) pair: the softmax weights of the key head's query heads are
+// applied to the values of value head `vh`, any of the num_kv, and the 32-bit results go to `parts`
+// [token][head][value head][D] (what mixing the weights across heads needs); `out` is not written.
+template <int D, bool CAP, bool PARTS>
 __global__ void __launch_bounds__(PRE_WARPS * 32, 2)
 prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_stride, __nv_bfloat16* __restrict__ out,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_slots,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len, int num_requests, int num_q,
                          int num_kv, int page_size, int window, float scale_log2, long long num_pages, int* status,
-                         int keep_first) {
+                         int keep_first, float cap_pre, float* __restrict__ parts) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -90,13 +100,15 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // A 1-D grid, numbered so that consecutive blocks are the same token tile of all kv heads: the block
   // scheduler then starts the heaviest tiles of EVERY head first (longest work first keeps the SMs level).
-  const int kh = (int)(blockIdx.x % num_kv);
+  const int pairs = PARTS ? num_kv * num_kv : num_kv;
+  const int kh = PARTS ? (int)(blockIdx.x % pairs) / num_kv : (int)(blockIdx.x % num_kv);
+  const int vh = PARTS ? (int)(blockIdx.x % pairs) % num_kv : kh;
   const int G = num_q / num_kv;
   const int tpt = PRE_M / G;  // tokens per block
 
   // ---- which request and which of its token tiles is this block? --------------------
   // Blocks are numbered from the back: the last tiles of a prompt see the most keys and start first.
-  const int tile_id = (int)(gridDim.x / num_kv) - 1 - (int)(blockIdx.x / num_kv);
+  const int tile_id = (int)(gridDim.x / pairs) - 1 - (int)(blockIdx.x / pairs);
   int r = -1, first = 0, q_len = 0, q_begin = 0;
   {
     int running = 0;
@@ -122,7 +134,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
   if (kvl <= 0 || p0 < 0) {                          // padding request: zeros
     for (int i = tid; i < rows_valid * D; i += blockDim.x) {
       const int row = i / D, d = i - row * D;
-      out[((long long)(q_begin + first + row / G) * num_q + kh * G + row % G) * D + d] = __float2bfloat16_rn(0.f);
+      const long long th = (long long)(q_begin + first + row / G) * num_q + kh * G + row % G;
+      if (PARTS) parts[(th * num_kv + vh) * D + d] = 0.f;
+      else out[th * D + d] = __float2bfloat16_rn(0.f);
     }
     return;
   }
@@ -170,7 +184,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
       const long long off = ok ? (s * kv_row + (long long)kh * D + ch * 8) : 0;
       const int sw = row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16);
       pre_cp_async_16(kbuf + sw, k_cache + off, ok);
-      pre_cp_async_16(vbuf + sw, v_cache + off, ok);
+      pre_cp_async_16(vbuf + sw, v_cache + (PARTS && ok ? off + (long long)(vh - kh) * D : off), ok);
     }
   };
 
@@ -244,6 +258,14 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
       // Scores stay raw (unscaled) until the exponential: p = 2^(s * scale_log2 - m), one fused
       // multiply-add and one ex2 per element; m is kept in scaled units.  Only tiles that touch the
       // diagonal, a window's edge or padding rows run the mask.
+      if (CAP) {
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int t = 0; t < NT_S; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[mt][t][e] = pre_tanh(sc[mt][t][e] * cap_pre);
+      }
       const bool need_mask = sink || !warp_full || kb + PRE_N - 1 > wp_min || (window > 0 && kb < wp_max - window + 1);
       float alpha[2][2];
 #pragma unroll
@@ -331,40 +353,48 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_st
       const float inv = ls > 0.f ? 1.f / ls : 0.f;
       const int row = wrow + mt * 16 + (lane >> 2) + h * 8;
       if (row < rows_valid) {
-        __nv_bfloat16* op = out + ((long long)(q_begin + first + row / G) * num_q + kh * G + row % G) * D;
+        const long long th = (long long)(q_begin + first + row / G) * num_q + kh * G + row % G;
+        if (PARTS) {
+          float* pp = parts + (th * num_kv + vh) * D;
 #pragma unroll
-        for (int j = 0; j < NT_O; ++j)
-          *reinterpret_cast<unsigned*>(op + j * 8 + c) = pre_pack(o[mt][j][2 * h] * inv, o[mt][j][2 * h + 1] * inv);
+          for (int j = 0; j < NT_O; ++j)
+            *reinterpret_cast<float2*>(pp + j * 8 + c) = make_float2(o[mt][j][2 * h] * inv, o[mt][j][2 * h + 1] * inv);
+        } else {
+          __nv_bfloat16* op = out + th * D;
+#pragma unroll
+          for (int j = 0; j < NT_O; ++j)
+            *reinterpret_cast<unsigned*>(op + j * 8 + c) = pre_pack(o[mt][j][2 * h] * inv, o[mt][j][2 * h + 1] * inv);
+        }
       }
     }
   }
 }
 
-static int g_prefill_attr_set[2] = {0, 0};
-
-template <int D>
-static int launch_prefill(int which, const void* q, long long q_row_stride, void* out, const void* k_cache,
+template <int D, bool CAP, bool PARTS>
+static int launch_prefill(const void* q, long long q_row_stride, void* out, const void* k_cache,
                           const void* v_cache, const int* block_table, int max_pages, const int* req_slots,
                           const int* cu_q, const int* kv_len, int tokens, int num_requests, int num_q, int num_kv,
                           int page_size, int window, float scale, long long num_pages, int* status, cudaStream_t st,
-                          int keep_first) {
+                          int keep_first, float softcap, float* parts) {
   using S = PrefillSmem<D>;
-  if (!g_prefill_attr_set[which]) {
-    if (cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::BYTES) !=
-        cudaSuccess)
+  static int attr_set = 0;  // (one flag per instantiation)
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(prefill_attention_kernel<D, CAP, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             S::BYTES) != cudaSuccess)
       return ULLM_ERR_LAUNCH;
-    cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(prefill_attention_kernel<D, CAP, PARTS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
-    g_prefill_attr_set[which] = 1;
+    attr_set = 1;
   }
   const int tpt = PRE_M / (num_q / num_kv);
   // at most ceil(tokens / tpt) + num_requests token tiles exist, however the tokens are spread
-  dim3 grid(((tokens + tpt - 1) / tpt + num_requests) * num_kv);
-  return ullm_launch_kernel(prefill_attention_kernel<D>, grid, dim3(PRE_WARPS * 32), (size_t)S::BYTES, st,
+  dim3 grid(((tokens + tpt - 1) / tpt + num_requests) * num_kv * (PARTS ? num_kv : 1));
+  const float log2e = 1.4426950408889634f;
+  return ullm_launch_kernel(prefill_attention_kernel<D, CAP, PARTS>, grid, dim3(PRE_WARPS * 32), (size_t)S::BYTES, st,
       (const __nv_bfloat16*)q, q_row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache,
       (const __nv_bfloat16*)v_cache, block_table, max_pages, req_slots, cu_q, kv_len, num_requests, num_q, num_kv,
-      page_size, window, scale * 1.4426950408889634f, num_pages, status, window > 0 ? keep_first : 0);
-  return ullm_launch_status();
+      page_size, window, CAP ? softcap * log2e : scale * log2e, num_pages, status, window > 0 ? keep_first : 0,
+      CAP ? scale / softcap : 0.f, parts);
 }
 
 // Sizes this kernel takes: bfloat16, head_dim 64 or 128, at most 32 query heads per kv head.
@@ -373,22 +403,44 @@ extern "C" int ullm_prefill_attention_supported(int head_dim, int num_q, int num
   return (head_dim == 64 || head_dim == 128) && (num_q / num_kv) <= 32;
 }
 
-// `keep_first`: with a window, the positions below it stay visible.
+// `keep_first`: with a window, the positions below it stay visible.  `softcap` > 0: capped scores.  `parts`
+// non-null (32-bit [tokens][heads][kv heads][head_dim]): every head's weights on every kv head's values, for
+// `ullm_mix_heads`; `out` is then unused.
+extern "C" int ullm_prefill_attention_ex(const void* q, long long q_row_stride, void* out, const void* k_cache,
+                                         const void* v_cache, const int* block_table, int max_pages,
+                                         const int* req_slots, const int* cu_q, const int* kv_len, int tokens,
+                                         int num_requests, int num_q, int num_kv, int head_dim, int page_size,
+                                         int window, float scale, long long num_pages, int* status, void* stream,
+                                         int keep_first, float softcap, float* parts) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || num_requests <= 0 || num_q <= 0 || num_kv <= 0 || page_size <= 0 || max_pages <= 0 || window < 0 ||
+      keep_first < 0 || softcap < 0.f)
+    return ULLM_ERR_BAD_SIZE;
+  if (!ullm_prefill_attention_supported(head_dim, num_q, num_kv)) return ULLM_ERR_UNSUPPORTED;
+  if (softcap > 0.f && parts != nullptr) return ULLM_ERR_UNSUPPORTED;
+  if (tokens == 0) return ULLM_OK;
+#define PRE_ARGS                                                                                                  \
+  q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len, tokens, num_requests,  \
+      num_q, num_kv, page_size, window, scale, num_pages, status, st, keep_first, softcap, parts
+  if (head_dim == 64) {
+    if (parts != nullptr) return launch_prefill<64, false, true>(PRE_ARGS);
+    if (softcap > 0.f) return launch_prefill<64, true, false>(PRE_ARGS);
+    return launch_prefill<64, false, false>(PRE_ARGS);
+  }
+  if (parts != nullptr) return launch_prefill<128, false, true>(PRE_ARGS);
+  if (softcap > 0.f) return launch_prefill<128, true, false>(PRE_ARGS);
+  return launch_prefill<128, false, false>(PRE_ARGS);
+#undef PRE_ARGS
+}
+
 extern "C" int ullm_prefill_attention_kept(const void* q, long long q_row_stride, void* out, const void* k_cache,
                                       const void* v_cache, const int* block_table, int max_pages, const int* req_slots,
                                       const int* cu_q, const int* kv_len, int tokens, int num_requests, int num_q,
                                       int num_kv, int head_dim, int page_size, int window, float scale,
                                       long long num_pages, int* status, void* stream, int keep_first) {
-  cudaStream_t st = (cudaStream_t)stream;
-  if (tokens < 0 || num_requests <= 0 || num_q <= 0 || num_kv <= 0 || page_size <= 0 || max_pages <= 0 || window < 0 || keep_first < 0)
-    return ULLM_ERR_BAD_SIZE;
-  if (!ullm_prefill_attention_supported(head_dim, num_q, num_kv)) return ULLM_ERR_UNSUPPORTED;
-  if (tokens == 0) return ULLM_OK;
-  if (head_dim == 64)
-    return launch_prefill<64>(0, q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
-                              tokens, num_requests, num_q, num_kv, page_size, window, scale, num_pages, status, st, keep_first);
-  return launch_prefill<128>(1, q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
-                             tokens, num_requests, num_q, num_kv, page_size, window, scale, num_pages, status, st, keep_first);
+  return ullm_prefill_attention_ex(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                   kv_len, tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale,
+                                   num_pages, status, stream, keep_first, 0.f, nullptr);
 }
 
 extern "C" int ullm_prefill_attention(const void* q, long long q_row_stride, void* out, const void* k_cache,

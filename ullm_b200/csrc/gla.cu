@@ -9,101 +9,158 @@
 // The recurrence runs token by token, so a request's result does not depend on how its tokens were cut into steps
 // or on what else is in the batch.  The parallelism is over requests, heads and the columns of S: a block owns
 // (request, head, a tile of columns); a column's d rows are spread over `rs` neighbouring lanes (row r belongs to
-// lane r mod rs), which meet in shuffles for the read-out.  q, k, the decays and the tile's v of a chunk of tokens
-// are staged in shared memory by all threads (the decays are evaluated there, once per block), then the chunk is
-// run from shared memory.
+// lane r mod rs), which meet in shuffles for the read-out.  A first kernel turns the decay's projection into the
+// decays (once per token and channel); q, k, the decays and the tile's v of a chunk of tokens are staged in shared
+// memory by a second set of threads of the block while the first set runs the chunk before (two buffers).
 //
 // State row layout (floats): S^T as [heads][dv][d].
 #include "common.cuh"
 
-#define GLA_THREADS 128
+#define GLA_THREADS 128    // threads that run the recurrence; as many again stage the next chunk
 #define GLA_MAX_DIM 512
-#define GLA_RPT 16  // rows of S a thread holds at most: 32 lanes x 16
+#define GLA_RPT 16         // rows of S a thread holds at most: 32 lanes x 16
 
 __device__ __forceinline__ float gla_log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename T, int RPT>
-__global__ void __launch_bounds__(GLA_THREADS)
+// z (32-bit, rows `stride` apart) <- exp(logsigmoid(z + bias) / tau) in place: the decays, evaluated once per
+// token and channel in front of the recurrence, whose blocks would otherwise each evaluate them again.
+__global__ void gla_decay_kernel(float* __restrict__ z, long long stride, const float* __restrict__ bias, int cols,
+                                 long long total, float inv_tau) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / cols;
+  const int c = (int)(i - t * cols);
+  float* p = z + t * stride + c;
+  *p = expf(gla_log_sigmoid(*p + (bias != nullptr ? bias[c] : 0.f)) * inv_tau);
+}
+
+// Threads 0 .. 127 run the recurrence on the chunk of tokens that lies in one half of shared memory while threads
+// 128 .. 255 stage the next chunk (q scaled, k, the decays, the tile's v; 32-bit) in the other half.  A staged row
+// is padded to RPT * rs entries with q = k = decay = 0, so the row loop has no bounds checks: the padded rows of S
+// stay zero.  CPT: neighbouring value columns a thread holds; the q, k and decay it reads serve all of them.
+template <typename T, int RPT, int CPT>
+__global__ void __launch_bounds__(2 * GLA_THREADS)
 gla_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off, int k_off, int v_off,
-                      const float* __restrict__ z, long long z_stride, const float* __restrict__ z_bias,
-                      float inv_tau, float q_scale, float* __restrict__ state, long long state_stride,
-                      const int* __restrict__ cu_q, const int* __restrict__ req_slots,
-                      const int* __restrict__ token_req, float* __restrict__ out, int heads, int dim, int vdim,
-                      int rs, int chunk, int num_slots, int* status) {
+                      const float* __restrict__ decay, long long decay_stride, float q_scale,
+                      float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
+                      const int* __restrict__ req_slots, const int* __restrict__ token_req, float* __restrict__ out,
+                      int heads, int dim, int vdim, int rs, int chunk, int num_slots, int* status) {
   extern __shared__ float sm[];
   pdl_launch_dependents();
   pdl_wait();
   const int req = blockIdx.z, head = blockIdx.y;
-  const int cols_per_block = GLA_THREADS / rs;
-  const int tid = threadIdx.x;
+  const int groups = GLA_THREADS / rs;       // column groups of a block
+  const int cols_per_block = groups * CPT;
+  const bool loader = threadIdx.x >= GLA_THREADS;
+  const int tid = threadIdx.x & (GLA_THREADS - 1);
   const int lane_row = tid % rs;
-  const int col_in_block = tid / rs;
-  const int col = blockIdx.x * cols_per_block + col_in_block;
-  const bool col_ok = col < vdim;
+  const int group = tid / rs;
+  const int col0 = blockIdx.x * cols_per_block;
+  const int col = col0 + group * CPT;        // the thread's first column
+  const int dimp = RPT * rs;                 // a staged row, padded
   const int t0 = cu_q[req], t1 = cu_q[req + 1];
   if (t1 <= t0) return;
   if (token_req[t0] < 0) {  // a row that belongs to no request: zeros out, no state touched
-    if (lane_row == 0 && col_ok)
-      for (int t = t0; t < t1; ++t) out[((long long)t * heads + head) * vdim + col] = 0.f;
+    if (!loader && lane_row == 0)
+      for (int t = t0; t < t1; ++t)
+        for (int c = 0; c < CPT; ++c)
+          if (col + c < vdim) out[((long long)t * heads + head) * vdim + col + c] = 0.f;
     return;
   }
   const int slot = req_slots[req];
   if (slot < 0 || slot >= num_slots) {
-    if (tid == 0) ullm_report(status, ULLM_STATUS_SLOT, req, slot);
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, req, slot);
     return;
   }
-  float* sq = sm;                    // [chunk][dim]
-  float* sk = sq + chunk * dim;      // [chunk][dim]
-  float* sa = sk + chunk * dim;      // [chunk][dim]
-  float* sv = sa + chunk * dim;      // [chunk][cols_per_block]
-  float* st_col = state + (long long)slot * state_stride + ((long long)head * vdim + (col_ok ? col : 0)) * dim;
+  const int buf_floats = chunk * (3 * dimp + cols_per_block);
+  float* st_head = state + (long long)slot * state_stride + (long long)head * vdim * dim;
 
-  float S[RPT];
-#pragma unroll
-  for (int i = 0; i < RPT; ++i) {
-    const int r = lane_row + i * rs;
-    S[i] = (col_ok && r < dim) ? st_col[r] : 0.f;
-  }
-  const int col0 = blockIdx.x * cols_per_block;
-  for (int c0 = t0; c0 < t1; c0 += chunk) {
-    const int cn = min(chunk, t1 - c0);
-    __syncthreads();  // the chunk before has been read
-    for (int i = tid; i < cn * dim; i += GLA_THREADS) {
-      const int t = i / dim, r = i - t * dim;
-      const T* row = qkv + (long long)(c0 + t) * row_stride + head * dim + r;
-      sq[i] = to_f32(row[q_off]) * q_scale;
-      sk[i] = to_f32(row[k_off]);
-      const float zz = z[(long long)(c0 + t) * z_stride + head * dim + r] + (z_bias != nullptr ? z_bias[head * dim + r] : 0.f);
-      sa[i] = expf(gla_log_sigmoid(zz) * inv_tau);
+  auto fill = [&](int which, int c0, int cn) {  // loader threads: tokens c0 .. c0 + cn - 1 into buffer `which`
+    float* sq = sm + which * buf_floats;  // [chunk][dimp]
+    float* sk = sq + chunk * dimp;
+    float* sa = sk + chunk * dimp;
+    float* sv = sa + chunk * dimp;        // [chunk][cols_per_block]
+    for (int i = tid; i < cn * dimp; i += GLA_THREADS) {
+      const int t = i / dimp, r = i - t * dimp;
+      float qv = 0.f, kv = 0.f, av = 0.f;
+      if (r < dim) {
+        const T* row = qkv + (long long)(c0 + t) * row_stride + head * dim + r;
+        qv = to_f32(row[q_off]) * q_scale;
+        kv = to_f32(row[k_off]);
+        av = decay[(long long)(c0 + t) * decay_stride + head * dim + r];
+      }
+      sq[i] = qv;
+      sk[i] = kv;
+      sa[i] = av;
     }
     for (int i = tid; i < cn * cols_per_block; i += GLA_THREADS) {
       const int t = i / cols_per_block, c = i - t * cols_per_block;
       sv[i] = (col0 + c < vdim) ? to_f32(qkv[(long long)(c0 + t) * row_stride + v_off + head * vdim + col0 + c]) : 0.f;
     }
-    __syncthreads();
-    for (int t = 0; t < cn; ++t) {
-      const float v = sv[t * cols_per_block + col_in_block];
-      const float* q = sq + t * dim;
-      const float* k = sk + t * dim;
-      const float* a = sa + t * dim;
-      float acc = 0.f;
-#pragma unroll
-      for (int i = 0; i < RPT; ++i) {
-        const int r = lane_row + i * rs;
-        if (r < dim) {
-          S[i] = a[r] * S[i] + k[r] * v;
-          acc += S[i] * q[r];
-        }
-      }
-      for (int o = rs >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane_row == 0 && col_ok) out[((long long)(c0 + t) * heads + head) * vdim + col] = acc;
-    }
-  }
-  if (col_ok) {
+  };
+
+  float S[RPT][CPT];
+  if (!loader) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
       const int r = lane_row + i * rs;
-      if (r < dim) st_col[r] = S[i];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) S[i][c] = (col + c < vdim && r < dim) ? st_head[(long long)(col + c) * dim + r] : 0.f;
+    }
+  } else {
+    fill(0, t0, min(chunk, t1 - t0));
+  }
+  __syncthreads();
+  int which = 0;
+  for (int c0 = t0; c0 < t1; c0 += chunk, which ^= 1) {
+    const int cn = min(chunk, t1 - c0);
+    if (loader) {
+      if (c0 + chunk < t1) fill(which ^ 1, c0 + chunk, min(chunk, t1 - c0 - chunk));
+    } else {
+      const float* sq = sm + which * buf_floats;
+      const float* sk = sq + chunk * dimp;
+      const float* sa = sk + chunk * dimp;
+      const float* sv = sa + chunk * dimp;
+      for (int t = 0; t < cn; ++t) {
+        float v[CPT], acc[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          v[c] = sv[t * cols_per_block + group * CPT + c];
+          acc[c] = 0.f;
+        }
+        const float* q = sq + t * dimp + lane_row;
+        const float* k = sk + t * dimp + lane_row;
+        const float* a = sa + t * dimp + lane_row;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+          const float ai = a[i * rs], ki = k[i * rs], qi = q[i * rs];
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) {
+            S[i][c] = fmaf(ai, S[i][c], ki * v[c]);
+            acc[c] = fmaf(S[i][c], qi, acc[c]);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+          for (int o = rs >> 1; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+        if (lane_row == 0) {
+#pragma unroll
+          for (int c = 0; c < CPT; ++c)
+            if (col + c < vdim) out[((long long)(c0 + t) * heads + head) * vdim + col + c] = acc[c];
+        }
+      }
+    }
+    __syncthreads();  // the next chunk is staged, this one has been read
+  }
+  if (!loader) {
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      const int r = lane_row + i * rs;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c)
+        if (col + c < vdim && r < dim) st_head[(long long)(col + c) * dim + r] = S[i][c];
     }
   }
 }
@@ -122,43 +179,66 @@ extern "C" int ullm_gla_supported(int heads, int dim, int vdim) {
 extern "C" long long ullm_gla_state_floats(int heads, int dim, int vdim) { return (long long)heads * vdim * dim; }
 
 template <typename T>
-static int gla_launch(const void* qkv, long long row_stride, int q_off, int k_off, int v_off, const float* z,
+static int gla_launch(const void* qkv, long long row_stride, int q_off, int k_off, int v_off, float* z,
                       long long z_stride, const float* z_bias, float inv_tau, float q_scale, float* state,
                       long long state_stride, const int* cu_q, const int* req_slots, const int* token_req, float* out,
-                      int requests, int heads, int dim, int vdim, int num_slots, int* status, cudaStream_t st) {
+                      int tokens, int requests, int heads, int dim, int vdim, int num_slots, int* status, cudaStream_t st) {
+  const long long total = (long long)tokens * heads * dim;
+  if (total > 0) {
+    const long long blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
+    const int rc = ullm_launch_kernel(gla_decay_kernel, dim3((int)blocks), dim3(256), 0, st, z, z_stride, z_bias,
+                                      heads * dim, total, inv_tau);
+    if (rc != ULLM_OK) return rc;
+  }
   const int rs = gla_rs(dim);
-  const int cpb = GLA_THREADS / rs;
-  int chunk = 8192 / (3 * dim + cpb);  // at most 32 KB of shared memory
-  chunk = chunk < 1 ? 1 : (chunk > 32 ? 32 : chunk);
-  const size_t smem = (size_t)chunk * (3 * dim + cpb) * sizeof(float);
-  const dim3 grid((vdim + cpb - 1) / cpb, heads, requests), block(GLA_THREADS);
+  const int groups = GLA_THREADS / rs;
   const int rows = (dim + rs - 1) / rs;
-#define GLA_GO(RPT)                                                                                                 \
-  return ullm_launch_kernel(gla_recurrence_kernel<T, RPT>, grid, block, smem, st, (const T*)qkv, row_stride, q_off,  \
-                            k_off, v_off, z, z_stride, z_bias, inv_tau, q_scale, state, state_stride, cu_q, req_slots, \
-                            token_req, out, heads, dim, vdim, rs, chunk, num_slots, status)
-  if (rows <= 4) GLA_GO(4);
-  if (rows <= 8) GLA_GO(8);
-  GLA_GO(GLA_RPT);
+  const int rpt = rows <= 4 ? 4 : (rows <= 8 ? 8 : GLA_RPT);
+  // two columns per thread where that still leaves two blocks for every SM
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long blocks2 = (long long)((vdim + 2 * groups - 1) / (2 * groups)) * heads * requests;
+  const int cpt = (rpt <= 8 && blocks2 >= 2LL * sms) ? 2 : 1;
+  const int cpb = groups * cpt;
+  const int dimp = rpt * rs;
+  int chunk = (40 * 1024 / 4) / (2 * (3 * dimp + cpb));  // two buffers in at most 40 KB of shared memory
+  chunk = chunk < 1 ? 1 : (chunk > 32 ? 32 : chunk);
+  const size_t smem = (size_t)2 * chunk * (3 * dimp + cpb) * sizeof(float);
+  const dim3 grid((vdim + cpb - 1) / cpb, heads, requests), block(2 * GLA_THREADS);
+#define GLA_GO(RPT, CPT)                                                                                              \
+  return ullm_launch_kernel(gla_recurrence_kernel<T, RPT, CPT>, grid, block, smem, st, (const T*)qkv, row_stride,      \
+                            q_off, k_off, v_off, (const float*)z, z_stride, q_scale, state, state_stride, cu_q,        \
+                            req_slots, token_req, out, heads, dim, vdim, rs, chunk, num_slots, status)
+  if (rpt == 4) {
+    if (cpt == 2) GLA_GO(4, 2);
+    GLA_GO(4, 1);
+  }
+  if (rpt == 8) {
+    if (cpt == 2) GLA_GO(8, 2);
+    GLA_GO(8, 1);
+  }
+  GLA_GO(GLA_RPT, 1);
 #undef GLA_GO
 }
 
 // qkv [tokens, *]: q and k (heads x dim) and v (heads x vdim) at the given column offsets of rows `row_stride`
-// apart; z [tokens, heads * dim] 32-bit (rows `z_stride` apart), `z_bias` [heads * dim] or null;
-// out [tokens, heads * vdim] 32-bit.
+// apart; z [tokens, heads * dim] 32-bit (rows `z_stride` apart), `z_bias` [heads * dim] or null: the decay's
+// projection, REPLACED by the decays; out [tokens, heads * vdim] 32-bit.
 extern "C" int ullm_gla_recurrence(int dtype, const void* qkv, long long row_stride, int q_off, int k_off, int v_off,
-                                   const float* z, long long z_stride, const float* z_bias, float inv_tau,
+                                   float* z, long long z_stride, const float* z_bias, float inv_tau,
                                    float q_scale, float* state, long long state_stride, const int* cu_q,
-                                   const int* req_slots, const int* token_req, float* out, int requests, int heads,
-                                   int dim, int vdim, int num_slots, int* status, void* stream) {
+                                   const int* req_slots, const int* token_req, float* out, int tokens, int requests,
+                                   int heads, int dim, int vdim, int num_slots, int* status, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  if (requests < 0 || heads <= 0 || dim <= 0 || vdim <= 0 || num_slots <= 0) return ULLM_ERR_BAD_SIZE;
+  if (requests < 0 || tokens < 0 || heads <= 0 || dim <= 0 || vdim <= 0 || num_slots <= 0) return ULLM_ERR_BAD_SIZE;
   if (dim > GLA_MAX_DIM || heads > 65535 || requests > 65535) return ULLM_ERR_UNSUPPORTED;
   if (state_stride < (long long)heads * vdim * dim) return ULLM_ERR_BAD_SIZE;
   if (requests == 0) return ULLM_OK;
 #define GLA_ARGS                                                                                                     \
   qkv, row_stride, q_off, k_off, v_off, z, z_stride, z_bias, inv_tau, q_scale, state, state_stride, cu_q, req_slots, \
-      token_req, out, requests, heads, dim, vdim, num_slots, status, st
+      token_req, out, tokens, requests, heads, dim, vdim, num_slots, status, st
   if (dtype == ULLM_DTYPE_F32) return gla_launch<float>(GLA_ARGS);
   if (dtype == ULLM_DTYPE_BF16) return gla_launch<__nv_bfloat16>(GLA_ARGS);
   if (dtype == ULLM_DTYPE_F16) return gla_launch<__half>(GLA_ARGS);

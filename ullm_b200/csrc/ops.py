@@ -133,7 +133,7 @@ class Kernels:
                 "ULLM_B200_FUSE_DECODE_ROPE", "ULLM_B200_MIXED_DECODE_ROWS", "ULLM_B200_DECODE_TC",
                 "ULLM_B200_DECODE_BALANCED", "ULLM_B200_SMALL_M_LINEAR", "ULLM_B200_STREAM_WEIGHT_MB",
                 "ULLM_B200_FUSED_MLP_ROWS", "ULLM_B200_LT_ROWS", "ULLM_B200_FUSED_TAIL_ROWS",
-                "ULLM_B200_STREAM_ALL_ROWS", "ULLM_B200_CHAIN_NORMS")
+                "ULLM_B200_STREAM_ALL_ROWS", "ULLM_B200_CHAIN_NORMS", "ULLM_B200_GENERAL_ATTN_TC")
 
     def apply_switches(self, env) -> None:
         """Sets every kernel choice from `env` (a mapping; the process environment at start-up): a switch that is
@@ -153,6 +153,9 @@ class Kernels:
         # brings more than one tile, else one), "pair" / "single" one of them always, "0" the mma.sync kernel
         self.tc_attention_mode = get("ULLM_B200_TC_ATTN", "1")
         self.use_tcgen05_attention = self.tc_attention_mode != "0"
+        # attention with capped scores or mixed heads (the general path of parts/attention.py) on the tensor-core
+        # kernels where the sizes allow; 0: the general kernel always
+        self.general_attention_tc = get("ULLM_B200_GENERAL_ATTN_TC", "1") != "0"
         # the splits of a request's keys merge inside a thread-block cluster (at most 8 splits) instead of through
         # scratch arrays and a second kernel
         # ("auto": for steps of at most 8 rows; "1" / "0": always / never, with `decode_split_target` splits)
@@ -219,6 +222,8 @@ class Kernels:
             "ullm_prefill_attention": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_kept": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P, I],
             "ullm_decode_attention_kept": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, I],
+            "ullm_decode_attention_capped": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, I, F],
+            "ullm_prefill_attention_ex": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P, I, F, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_pair": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
@@ -247,7 +252,7 @@ class Kernels:
             "ullm_paged_attention_generic_ex2": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I,
                                                  F, P],
             "ullm_mix_heads": [I, P, P, P, I, I, I, I, P],
-            "ullm_gla_recurrence": [I, P, LL, I, I, I, P, LL, P, F, F, P, LL, P, P, P, P, I, I, I, I, I, P, P],
+            "ullm_gla_recurrence": [I, P, LL, I, I, I, P, LL, P, F, F, P, LL, P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_head_norm_gate": [I, P, P, LL, P, P, I, I, I, F, I, I, P],
             "ullm_moe_route": [P, P, P, I, I, I, I, I, P],
             "ullm_moe_arrange": [P, I, I, P, P, P, P],
@@ -879,7 +884,8 @@ class Kernels:
                        out, requests, heads, dim, vdim):
         """The recurrence of csrc/gla.cu over the step's tokens, from and into the requests' state rows.
         qkv [T, *]: q, k, v at the given column offsets; z [T, heads * dim] float32 (the decay's projection, a view
-        with any row stride), `z_bias` float32 [heads * dim] or None; out [T, heads * vdim] float32."""
+        with any row stride; the kernel REPLACES it by the decays), `z_bias` float32 [heads * dim] or None;
+        out [T, heads * vdim] float32."""
         _need(qkv, "qkv")
         _need(z, "z", torch.float32, contiguous=False)
         _need(state, "state", torch.float32)
@@ -898,7 +904,7 @@ class Kernels:
         self._check(self.lib.ullm_gla_recurrence(
             _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), q_off, k_off, v_off, _ptr(z), z.stride(0), _ptr(z_bias),
             float(inv_tau), float(q_scale), _ptr(state), state.stride(0), _ptr(cu_q), _ptr(req_slots), _ptr(token_req),
-            _ptr(out), requests, heads, dim, vdim, state.shape[0], _ptr(self.status), _stream()),
+            _ptr(out), T, requests, heads, dim, vdim, state.shape[0], _ptr(self.status), _stream()),
             f"gla_recurrence (heads {heads}, dim {dim}, vdim {vdim})")
 
     # -- sub-layers added to a 32-bit stream through gates; a per-token side input ----------
@@ -1165,12 +1171,14 @@ class Kernels:
                                             qkv.stride(0)) == "split")
 
     def _decode_rows(self, qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
-                     page_size, window, scale, num_pages, ragged, ctx, fuse=None, keep_first: int = 0) -> None:
+                     page_size, window, scale, num_pages, ragged, ctx, fuse=None, keep_first: int = 0,
+                     softcap: float = 0.0) -> None:
         """Decode attention of T one-token rows (row i belongs to request row i): streams the pages once.
-        `keep_first` > 0 (with a window): the per-request split kernel, the one that takes kept first positions."""
+        `keep_first` > 0 (with a window) or `softcap` > 0 (capped scores): the per-request split kernel, the one
+        that takes them."""
         T = out.shape[0]
         choice = self._decode_choice(T, ragged, num_q, num_kv, head_dim, page_size, qkv.stride(0))
-        if keep_first > 0:
+        if keep_first > 0 or softcap > 0:
             choice = "split"
         if fuse is not None and choice != "split":
             raise KernelError("decode attention: q and k were left unprepared for a kernel that does not prepare them")
@@ -1232,6 +1240,12 @@ class Kernels:
                 _ptr(fuse["cos"]), _ptr(fuse["sin"]), fuse["cos"].shape[0], _ptr(fuse["positions"]),
                 _ptr(fuse["slot_mapping"]), _ptr(self.status), _stream()),
                 f"decode_attention_fused (head_dim {head_dim})")
+        elif softcap > 0:
+            self._check(self.lib.ullm_decode_attention_capped(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                _ptr(req_slots), _ptr(kv_len), _ptr(out), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
+                int(window), float(scale), splits, num_pages, _ptr(self.status), _stream(), int(keep_first),
+                float(softcap)), f"decode_attention (head_dim {head_dim}, cap {softcap})")
         elif keep_first > 0:
             self._check(self.lib.ullm_decode_attention_kept(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
@@ -1284,6 +1298,26 @@ class Kernels:
                 _need(parts, "parts", torch.float32)
                 if parts.shape != (T, num_q * num_kv * v_dim):
                     raise KernelError(f"paged_attention: parts {tuple(parts.shape)}")
+            # bfloat16 at head sizes 64 / 128 with values as wide as keys: the tensor-core kernels.  Decode steps
+            # without mixed heads stream their pages through the split decode kernel; everything else (prompt
+            # portions, mixed steps, and every step with mixed heads) runs the mma.sync prompt kernel
+            tc = (ctx is not None and qkv.dtype == torch.bfloat16 and v_dim == head_dim and self.general_attention_tc
+                  and self.lib.ullm_prefill_attention_supported(head_dim, num_q, num_kv)
+                  and not (softcap > 0 and parts is not None))
+            if (tc and parts is None and ctx.decode_only and T == ctx.num_requests
+                    and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)):
+                self._decode_rows(qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
+                                  page_size, window, scale, num_pages, False, ctx, None, keep_first, softcap)
+                return
+            if tc:
+                self._check(self.lib.ullm_prefill_attention_ex(
+                    _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                    block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, ctx.num_requests, num_q, num_kv,
+                    head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream(),
+                    int(keep_first), float(softcap), _ptr(parts)),
+                    f"prefill_attention (head_dim {head_dim}, cap {softcap}, parts {parts is not None})")
+                self.attention_path = "prefill"
+                return
             self.attention_path = "generic"
             self._check(self.lib.ullm_paged_attention_generic_ex2(
                 _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
