@@ -8,13 +8,16 @@
 //
 // The recurrence runs token by token, so a request's result does not depend on how its tokens were cut into steps
 // or on what else is in the batch.  The parallelism is over requests, heads and the columns of S: a block owns
-// (request, head, a tile of columns); a column's d rows are spread over `rs` neighbouring lanes (row r belongs to
-// lane r mod rs), which meet in shuffles for the read-out.  A first kernel turns the decay's projection into the
+// (request, head, a tile of columns); a column's d rows are spread over `rs` neighbouring lanes in pieces of four
+// (rows 4 (g rs + lane) .. + 3 belong to that lane: one 16-byte read of shared memory per piece and operand, free
+// of bank conflicts), which meet in shuffles for the read-out.  A first kernel turns the decay's projection into the
 // decays (once per token and channel); q, k, the decays and the tile's v of a chunk of tokens are staged in shared
 // memory by a second set of threads of the block while the first set runs the chunk before (two buffers).
 //
 // State row layout (floats): S^T as [heads][dv][d].
 #include "common.cuh"
+
+#include <type_traits>
 
 #define GLA_THREADS 128    // threads that run the recurrence; as many again stage the next chunk
 #define GLA_MAX_DIM 512
@@ -47,7 +50,7 @@ gla_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off
                       float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
                       const int* __restrict__ req_slots, const int* __restrict__ token_req, float* __restrict__ out,
                       int heads, int dim, int vdim, int rs, int chunk, int num_slots, int* status) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_launch_dependents();
   pdl_wait();
   const int req = blockIdx.z, head = blockIdx.y;
@@ -75,6 +78,9 @@ gla_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off
     return;
   }
   const int buf_floats = chunk * (3 * dimp + cols_per_block);
+  const bool vec8 = std::is_same<T, __nv_bfloat16>::value && (dim & 7) == 0 && (dimp & 7) == 0 && (q_off & 7) == 0 &&
+                    (k_off & 7) == 0 && (row_stride & 7) == 0 && (decay_stride & 3) == 0 &&
+                    (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(decay) & 15) == 0;
   float* st_head = state + (long long)slot * state_stride + (long long)head * vdim * dim;
 
   auto fill = [&](int which, int c0, int cn) {  // loader threads: tokens c0 .. c0 + cn - 1 into buffer `which`
@@ -82,6 +88,58 @@ gla_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off
     float* sk = sq + chunk * dimp;
     float* sa = sk + chunk * dimp;
     float* sv = sa + chunk * dimp;        // [chunk][cols_per_block]
+    if (vec8) {
+      // bfloat16 rows that allow 16-byte pieces: a thread moves 8 neighbouring entries of q, k and the decays per
+      // item, two items in flight
+      const int per_tok = dimp >> 3, n8 = cn * per_tok;
+      for (int g0 = tid; g0 < n8; g0 += 2 * GLA_THREADS) {
+        uint4 rq[2], rk[2];
+        float4 ra[2][2];
+        bool live[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int g = g0 + j * GLA_THREADS;
+          live[j] = false;
+          if (g < n8) {
+            const int t = g / per_tok, r = (g - t * per_tok) << 3;
+            if (r < dim) {
+              live[j] = true;
+              const T* row = qkv + (long long)(c0 + t) * row_stride + head * dim + r;
+              rq[j] = *reinterpret_cast<const uint4*>(row + q_off);
+              rk[j] = *reinterpret_cast<const uint4*>(row + k_off);
+              const float4* ap = reinterpret_cast<const float4*>(decay + (long long)(c0 + t) * decay_stride + head * dim + r);
+              ra[j][0] = ap[0];
+              ra[j][1] = ap[1];
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int g = g0 + j * GLA_THREADS;
+          if (g < n8) {
+            const int i = g << 3;
+            float4 a, b, c, d;
+            a = b = c = d = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live[j]) {
+              const __nv_bfloat16* eq = reinterpret_cast<const __nv_bfloat16*>(&rq[j]);
+              const __nv_bfloat16* ek = reinterpret_cast<const __nv_bfloat16*>(&rk[j]);
+              a = make_float4(__bfloat162float(eq[0]) * q_scale, __bfloat162float(eq[1]) * q_scale,
+                              __bfloat162float(eq[2]) * q_scale, __bfloat162float(eq[3]) * q_scale);
+              b = make_float4(__bfloat162float(eq[4]) * q_scale, __bfloat162float(eq[5]) * q_scale,
+                              __bfloat162float(eq[6]) * q_scale, __bfloat162float(eq[7]) * q_scale);
+              c = make_float4(__bfloat162float(ek[0]), __bfloat162float(ek[1]), __bfloat162float(ek[2]), __bfloat162float(ek[3]));
+              d = make_float4(__bfloat162float(ek[4]), __bfloat162float(ek[5]), __bfloat162float(ek[6]), __bfloat162float(ek[7]));
+            }
+            *reinterpret_cast<float4*>(sq + i) = a;
+            *reinterpret_cast<float4*>(sq + i + 4) = b;
+            *reinterpret_cast<float4*>(sk + i) = c;
+            *reinterpret_cast<float4*>(sk + i + 4) = d;
+            *reinterpret_cast<float4*>(sa + i) = live[j] ? ra[j][0] : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(sa + i + 4) = live[j] ? ra[j][1] : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+      }
+    } else
     for (int i = tid; i < cn * dimp; i += GLA_THREADS) {
       const int t = i / dimp, r = i - t * dimp;
       float qv = 0.f, kv = 0.f, av = 0.f;
@@ -105,7 +163,7 @@ gla_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off
   if (!loader) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-      const int r = lane_row + i * rs;
+      const int r = ((i >> 2) * rs + lane_row) * 4 + (i & 3);
 #pragma unroll
       for (int c = 0; c < CPT; ++c) S[i][c] = (col + c < vdim && r < dim) ? st_head[(long long)(col + c) * dim + r] : 0.f;
     }
@@ -123,32 +181,53 @@ gla_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off
       const float* sk = sq + chunk * dimp;
       const float* sa = sk + chunk * dimp;
       const float* sv = sa + chunk * dimp;
-      for (int t = 0; t < cn; ++t) {
-        float v[CPT], acc[CPT];
+      // Four tokens at a time: only S carries a dependence from token to token (one multiply-add per row); the
+      // read-outs of the four tokens are summed over the lanes together, so that a warp waits for one chain of
+      // shuffles per four tokens instead of one per token.
+      constexpr int TB = 4;
+      for (int t = 0; t < cn; t += TB) {
+        float acc[TB][CPT];
 #pragma unroll
-        for (int c = 0; c < CPT; ++c) {
-          v[c] = sv[t * cols_per_block + group * CPT + c];
-          acc[c] = 0.f;
-        }
-        const float* q = sq + t * dimp + lane_row;
-        const float* k = sk + t * dimp + lane_row;
-        const float* a = sa + t * dimp + lane_row;
+        for (int j = 0; j < TB; ++j) {
 #pragma unroll
-        for (int i = 0; i < RPT; ++i) {
-          const float ai = a[i * rs], ki = k[i * rs], qi = q[i * rs];
+          for (int c = 0; c < CPT; ++c) acc[j][c] = 0.f;
+          if (t + j < cn) {
+            float v[CPT];
 #pragma unroll
-          for (int c = 0; c < CPT; ++c) {
-            S[i][c] = fmaf(ai, S[i][c], ki * v[c]);
-            acc[c] = fmaf(S[i][c], qi, acc[c]);
+            for (int c = 0; c < CPT; ++c) v[c] = sv[(t + j) * cols_per_block + group * CPT + c];
+            const float4* q4 = reinterpret_cast<const float4*>(sq + (t + j) * dimp) + lane_row;
+            const float4* k4 = reinterpret_cast<const float4*>(sk + (t + j) * dimp) + lane_row;
+            const float4* a4 = reinterpret_cast<const float4*>(sa + (t + j) * dimp) + lane_row;
+#pragma unroll
+            for (int g = 0; g < RPT / 4; ++g) {
+              const float4 av = a4[g * rs], kv = k4[g * rs], qv = q4[g * rs];
+              const float ar[4] = {av.x, av.y, av.z, av.w}, kr[4] = {kv.x, kv.y, kv.z, kv.w},
+                          qr[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                  S[4 * g + e][c] = fmaf(ar[e], S[4 * g + e][c], kr[e] * v[c]);
+                  acc[j][c] = fmaf(S[4 * g + e][c], qr[e], acc[j][c]);
+                }
+              }
+            }
           }
         }
+        for (int o = rs >> 1; o > 0; o >>= 1) {
 #pragma unroll
-        for (int c = 0; c < CPT; ++c)
-          for (int o = rs >> 1; o > 0; o >>= 1) acc[c] += __shfl_xor_sync(0xffffffffu, acc[c], o);
+          for (int j = 0; j < TB; ++j)
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) acc[j][c] += __shfl_xor_sync(0xffffffffu, acc[j][c], o);
+        }
         if (lane_row == 0) {
 #pragma unroll
-          for (int c = 0; c < CPT; ++c)
-            if (col + c < vdim) out[((long long)(c0 + t) * heads + head) * vdim + col + c] = acc[c];
+          for (int j = 0; j < TB; ++j)
+            if (t + j < cn) {
+#pragma unroll
+              for (int c = 0; c < CPT; ++c)
+                if (col + c < vdim) out[((long long)(c0 + t + j) * heads + head) * vdim + col + c] = acc[j][c];
+            }
         }
       }
     }
@@ -157,7 +236,7 @@ gla_recurrence_kernel(const T* __restrict__ qkv, long long row_stride, int q_off
   if (!loader) {
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-      const int r = lane_row + i * rs;
+      const int r = ((i >> 2) * rs + lane_row) * 4 + (i & 3);
 #pragma unroll
       for (int c = 0; c < CPT; ++c)
         if (col + c < vdim && r < dim) st_head[(long long)(col + c) * dim + r] = S[i][c];
@@ -195,12 +274,23 @@ static int gla_launch(const void* qkv, long long row_stride, int q_off, int k_of
   const int groups = GLA_THREADS / rs;
   const int rows = (dim + rs - 1) / rs;
   const int rpt = rows <= 4 ? 4 : (rows <= 8 ? 8 : GLA_RPT);
-  // two columns per thread where that still leaves two blocks for every SM
+  // Columns per thread (1, 2 or 4): the recurrence is a chain per token, so the time is (waves of blocks) x (a
+  // token's cost, which grows slowly with the columns a thread holds); two blocks are resident per SM.
   int sms = 148;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long blocks2 = (long long)((vdim + 2 * groups - 1) / (2 * groups)) * heads * requests;
-  const int cpt = (rpt <= 8 && blocks2 >= 2LL * sms) ? 2 : 1;
+  int cpt = 1;
+  if (rpt <= 8) {
+    double best = 1e30;
+    for (int c = 1; c <= 4; c *= 2) {
+      const long long blocks = (long long)((vdim + c * groups - 1) / (c * groups)) * heads * requests;
+      const double cost = (double)((blocks + 2LL * sms - 1) / (2LL * sms)) * (1.0 + 0.25 * (c - 1));
+      if (cost < best - 1e-9) {
+        best = cost;
+        cpt = c;
+      }
+    }
+  }
   const int cpb = groups * cpt;
   const int dimp = rpt * rs;
   int chunk = (40 * 1024 / 4) / (2 * (3 * dimp + cpb));  // two buffers in at most 40 KB of shared memory
@@ -212,10 +302,12 @@ static int gla_launch(const void* qkv, long long row_stride, int q_off, int k_of
                             q_off, k_off, v_off, (const float*)z, z_stride, q_scale, state, state_stride, cu_q,        \
                             req_slots, token_req, out, heads, dim, vdim, rs, chunk, num_slots, status)
   if (rpt == 4) {
+    if (cpt == 4) GLA_GO(4, 4);
     if (cpt == 2) GLA_GO(4, 2);
     GLA_GO(4, 1);
   }
   if (rpt == 8) {
+    if (cpt == 4) GLA_GO(8, 4);
     if (cpt == 2) GLA_GO(8, 2);
     GLA_GO(8, 1);
   }
