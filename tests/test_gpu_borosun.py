@@ -333,7 +333,7 @@ def test_tensor_core_attention_agrees_with_the_general_kernel(tmp_path):
             K.general_attention_tc = on
             r = make_runner(tmp_path, cfg, w, page, "bfloat16", name=f"tc{on}")
             got[on] = replay(r, {"a": ids}, plan)["a"]
-            assert K.attention_path == ("prefill" if on else "generic")  # (the last layer mixes heads)
+            assert K.attention_path == ("decode" if on else "generic")
     finally:
         K.general_attention_tc = True
     ref = oracle(ids, w, cfg)

@@ -48,6 +48,10 @@ struct DecFuse {
   int keep_first;  // with a window: the positions below it stay visible (0: none)
   float cap_pre;   // capped scores, s <- cap * tanh(s * scale / cap): scale / cap here (0: no cap) ...
   float cap_post;  // ... and cap * log2(e) here
+  // parts non-null: grid.y counts (key head, VALUE head) pairs; the weights of the key head's query heads are
+  // applied to the values of any kv head, and the 32-bit results go to parts [request][head][value head][D]
+  // (what mixing the softmax weights across heads needs); `out` is not written
+  float* parts;
 };
 
 // 2^x by the hardware's unit alone (exp2f adds a range fix-up around the same instruction)
@@ -80,7 +84,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
   constexpr int NT_O = D / 8;          // n-tiles of the output
   using S = DecodeSmem<D>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int split = blockIdx.x, num_splits = gridDim.x, kh = blockIdx.y, b = blockIdx.z;
+  const int split = blockIdx.x, num_splits = gridDim.x, b = blockIdx.z;
+  const int kh = fu.parts != nullptr ? blockIdx.y / num_kv : blockIdx.y;  // key head
+  const int vh = fu.parts != nullptr ? blockIdx.y % num_kv : kh;          // value head
+  const int o_rep = fu.parts != nullptr ? num_kv : 1;
   const int group = num_q / num_kv;
   const int kvl = kv_len[b];
   const int pos = kvl - 1;
@@ -124,7 +131,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
       const long long off = ok ? (slot * kv_row + (long long)kh * D + ch * 8) : 0;
       const int sw = row * S::ROW_BYTES + ((ch ^ (row & 7)) * 16);
       cp_async_16(kbuf + sw, k_cache + off, ok);
-      cp_async_16(vbuf + sw, v_cache + off, ok);
+      cp_async_16(vbuf + sw, v_cache + (ok ? off + (long long)(vh - kh) * D : 0), ok);
     }
   };
 
@@ -436,8 +443,11 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
       acc += mo[(w * 16 + r) * (D + 2) + d] * f;
     }
     const int h = kh * group + r;
+    const long long orow = ((long long)b * num_q + h) * o_rep + (fu.parts != nullptr ? vh : 0);
     if (num_splits == 1) {
-      out[((long long)b * num_q + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      const float val = ll > 0.f ? acc / ll : 0.f;
+      if (fu.parts != nullptr) fu.parts[orow * D + d] = val;
+      else out[orow * D + d] = __float2bfloat16_rn(val);
     } else if (CL) {
       cm[r * (D + 2) + d] = acc;
       if (d == 0) {
@@ -445,7 +455,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
         cm[r * (D + 2) + D + 1] = ll;
       }
     } else {
-      const long long p = ((long long)b * num_q + h) * num_splits + split;
+      const long long p = orow * num_splits + split;
       part_o[p * D + d] = acc;
       if (d == 0) {
         part_ml[p * 2] = mm;
@@ -484,7 +494,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
         ll += ls[s2] * f;
         acc += as[s2] * f;
       }
-      out[((long long)b * num_q + kh * group + r) * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+      const long long orow = ((long long)b * num_q + kh * group + r) * o_rep + (fu.parts != nullptr ? vh : 0);
+      const float val = ll > 0.f ? acc / ll : 0.f;
+      if (fu.parts != nullptr) fu.parts[orow * D + d] = val;
+      else out[orow * D + d] = __float2bfloat16_rn(val);
     }
     cluster.sync();  // no block leaves while a peer may still read its partial
   }
@@ -493,7 +506,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, long long q_row_str
 // out[b, h, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, int num_splits) {
+                                    __nv_bfloat16* __restrict__ out, int num_splits, float* __restrict__ out_f32) {
   pdl_launch_dependents();
   pdl_wait();
   const long long bh = blockIdx.x;
@@ -528,7 +541,9 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
       acc += os[i] * f;
     }
   }
-  out[bh * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+  const float val = ll > 0.f ? acc / ll : 0.f;
+  if (out_f32 != nullptr) out_f32[bh * D + d] = val;  // (rows then count (request, head, value head))
+  else out[bh * D + d] = __float2bfloat16_rn(val);
 }
 
 static int g_decode_attr_set[2] = {0, 0};
@@ -559,7 +574,8 @@ static int launch_decode(int which, const void* q, long long q_row_stride, const
                          cudaSharedmemCarveoutMaxShared);
     g_decode_attr_set[which] = 1;
   }
-  dim3 grid(num_splits, num_kv, batch);
+  const int o_rep = fu.parts != nullptr ? num_kv : 1;
+  dim3 grid(num_splits, num_kv * o_rep, batch);
   g_decode_last_cluster = 0;
   if (g_decode_cluster == 1 && num_splits > 1 && num_splits <= 8) {
     cudaLaunchConfig_t cfg = {};
@@ -592,8 +608,8 @@ static int launch_decode(int which, const void* q, long long q_row_stride, const
       scale * 1.4426950408889634f, num_pages, status, fu);
   if (rc != ULLM_OK) return rc;
   if (num_splits > 1)
-    rc = ullm_launch_kernel(decode_merge_kernel<D>, dim3(batch * num_q), dim3(D), 0, st, (const float*)part_o,
-                            (const float*)part_ml, (__nv_bfloat16*)out, num_splits);
+    rc = ullm_launch_kernel(decode_merge_kernel<D>, dim3(batch * num_q * o_rep), dim3(D), 0, st, (const float*)part_o,
+                            (const float*)part_ml, (__nv_bfloat16*)out, num_splits, fu.parts);
   return rc;
 }
 
@@ -620,7 +636,8 @@ static int decode_attention_impl(const void* q, long long q_row_stride, const vo
   if (num_splits > 1 && scratch == nullptr) return ULLM_ERR_BAD_SIZE;
   if (batch == 0) return ULLM_OK;
   float* part_o = scratch;
-  float* part_ml = scratch != nullptr ? scratch + (long long)batch * num_q * num_splits * head_dim : nullptr;
+  const long long o_rows = (long long)batch * num_q * (fu.parts != nullptr ? num_kv : 1);
+  float* part_ml = scratch != nullptr ? scratch + o_rows * num_splits * head_dim : nullptr;
   if (head_dim == 64)
     return launch_decode<64>(0, q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out,
                              part_o, part_ml, batch, num_q, num_kv, page_size, window, scale, num_splits, num_pages,
@@ -670,6 +687,24 @@ extern "C" int ullm_decode_attention_capped(const void* q, long long q_row_strid
   return decode_attention_impl(q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, out, scratch,
                                batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits, num_pages, status,
                                stream, fu);
+}
+
+// Every head's softmax weights applied to EVERY kv head's values, unrounded, into `parts` (32-bit,
+// [batch][heads][kv heads][head_dim]) for `ullm_mix_heads`.  `scratch`: num_kv times the floats of
+// `ullm_decode_attention_scratch_floats`.
+extern "C" int ullm_decode_attention_parts(const void* q, long long q_row_stride, const void* k_cache,
+                                           const void* v_cache, const int* block_table, int max_pages,
+                                           const int* req_slots, const int* kv_len, float* parts, float* scratch,
+                                           int batch, int num_q, int num_kv, int head_dim, int page_size, int window,
+                                           float scale, int num_splits, long long num_pages, int* status,
+                                           void* stream, int keep_first) {
+  if (keep_first < 0 || parts == nullptr) return ULLM_ERR_BAD_SIZE;
+  DecFuse fu = {};
+  fu.keep_first = window > 0 ? keep_first : 0;
+  fu.parts = parts;
+  return decode_attention_impl(q, q_row_stride, k_cache, v_cache, block_table, max_pages, req_slots, kv_len, nullptr,
+                               scratch, batch, num_q, num_kv, head_dim, page_size, window, scale, num_splits,
+                               num_pages, status, stream, fu);
 }
 
 // The same with q, the new key and the new value taken as the projection left them: the kernel applies the

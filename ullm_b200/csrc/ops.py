@@ -223,6 +223,7 @@ class Kernels:
             "ullm_prefill_attention_kept": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P, I],
             "ullm_decode_attention_kept": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, I],
             "ullm_decode_attention_capped": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, I, F],
+            "ullm_decode_attention_parts": [P, LL, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, I, LL, P, P, I],
             "ullm_prefill_attention_ex": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P, I, F, P],
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_pair": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
@@ -1172,13 +1173,14 @@ class Kernels:
 
     def _decode_rows(self, qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
                      page_size, window, scale, num_pages, ragged, ctx, fuse=None, keep_first: int = 0,
-                     softcap: float = 0.0) -> None:
+                     softcap: float = 0.0, parts=None) -> None:
         """Decode attention of T one-token rows (row i belongs to request row i): streams the pages once.
-        `keep_first` > 0 (with a window) or `softcap` > 0 (capped scores): the per-request split kernel, the one
-        that takes them."""
-        T = out.shape[0]
+        `keep_first` > 0 (with a window), `softcap` > 0 (capped scores) or `parts` (every head's weights on every
+        kv head's values, 32-bit [T, num_q * num_kv * head_dim]; `out` unused): the per-request split kernel, the
+        one that takes them."""
+        T = qkv.shape[0]
         choice = self._decode_choice(T, ragged, num_q, num_kv, head_dim, page_size, qkv.stride(0))
-        if keep_first > 0 or softcap > 0:
+        if keep_first > 0 or softcap > 0 or parts is not None:
             choice = "split"
         if fuse is not None and choice != "split":
             raise KernelError("decode attention: q and k were left unprepared for a kernel that does not prepare them")
@@ -1214,20 +1216,22 @@ class Kernels:
         # merged by the second kernel.
         cluster = T <= max(8, self.stream_all_rows) if self.decode_cluster_merge == "auto" else self.decode_cluster_merge
         self.lib.ullm_decode_attention_cluster_merge(1 if cluster else 0)
+        pairs = num_kv * (num_kv if parts is not None else 1)  # (key head, value head) pairs a request brings
         if cluster and self.decode_cluster_merge == "auto":
             splits = 8
-            while splits > 1 and T * num_kv * splits > 2 * self.sm_count:
+            while splits > 1 and T * pairs * splits > 2 * self.sm_count:
                 splits //= 2
         else:
-            splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * num_kv))))
+            splits = max(1, min(8 if cluster else 32, -(-self.decode_split_target // (T * pairs))))
             # (request, kv head) pairs that fill half of the places on the SMs or more (two blocks per SM), but not
             # more than all of them, run unsplit: one wave, no merge launch (24 x 2,048 tokens, 8 kv heads: 46 us
             # against 50 with 3 splits and 58 with 2; 32 x 2,048: 52 against 61 with 2 splits)
-            if self.decode_cluster_merge == "auto" and self.sm_count <= T * num_kv <= 2 * self.sm_count:
+            if self.decode_cluster_merge == "auto" and self.sm_count <= T * pairs <= 2 * self.sm_count:
                 splits = 1
         # (splits x rows stays below the blocks aimed for, per kv head, plus one split per row)
-        most = num_q * (self.decode_split_target // num_kv + max(T, getattr(ctx.workspace, "max_requests", 0)))
-        scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * splits, head_dim + 2, torch.float32,
+        o_rep = num_kv if parts is not None else 1
+        most = num_q * o_rep * (self.decode_split_target // pairs + max(T, getattr(ctx.workspace, "max_requests", 0)))
+        scratch = ctx.workspace.get("attn.decode_scratch", T * num_q * o_rep * splits, head_dim + 2, torch.float32,
                                     reserve=most)
         if fuse is not None:
             for t, n in ((fuse["cos"], "cos table"), (fuse["sin"], "sin table")):
@@ -1240,6 +1244,12 @@ class Kernels:
                 _ptr(fuse["cos"]), _ptr(fuse["sin"]), fuse["cos"].shape[0], _ptr(fuse["positions"]),
                 _ptr(fuse["slot_mapping"]), _ptr(self.status), _stream()),
                 f"decode_attention_fused (head_dim {head_dim})")
+        elif parts is not None:
+            self._check(self.lib.ullm_decode_attention_parts(
+                _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
+                _ptr(req_slots), _ptr(kv_len), _ptr(parts), _ptr(scratch), T, num_q, num_kv, head_dim, page_size,
+                int(window), float(scale), splits, num_pages, _ptr(self.status), _stream(), int(keep_first)),
+                f"decode_attention (head_dim {head_dim}, parts)")
         elif softcap > 0:
             self._check(self.lib.ullm_decode_attention_capped(
                 _ptr(qkv), qkv.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
@@ -1299,15 +1309,15 @@ class Kernels:
                 if parts.shape != (T, num_q * num_kv * v_dim):
                     raise KernelError(f"paged_attention: parts {tuple(parts.shape)}")
             # bfloat16 at head sizes 64 / 128 with values as wide as keys: the tensor-core kernels.  Decode steps
-            # without mixed heads stream their pages through the split decode kernel; everything else (prompt
-            # portions, mixed steps, and every step with mixed heads) runs the mma.sync prompt kernel
+            # stream their pages through the split decode kernel; steps with prompt portions run the mma.sync
+            # prompt kernel
             tc = (ctx is not None and qkv.dtype == torch.bfloat16 and v_dim == head_dim and self.general_attention_tc
                   and self.lib.ullm_prefill_attention_supported(head_dim, num_q, num_kv)
                   and not (softcap > 0 and parts is not None))
-            if (tc and parts is None and ctx.decode_only and T == ctx.num_requests
+            if (tc and ctx.decode_only and T == ctx.num_requests
                     and self.lib.ullm_decode_attention_supported(head_dim, num_q, num_kv)):
                 self._decode_rows(qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
-                                  page_size, window, scale, num_pages, False, ctx, None, keep_first, softcap)
+                                  page_size, window, scale, num_pages, False, ctx, None, keep_first, softcap, parts)
                 return
             if tc:
                 self._check(self.lib.ullm_prefill_attention_ex(
