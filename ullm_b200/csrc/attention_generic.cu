@@ -134,23 +134,71 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
 
 // Softmax weights mixed across heads, w'_h = sum_g M[h][g] w_g, applied to head h's own values:
 // out[t][h] = sum_g M[h][g] * part[t][g][kv head of h], with part = every head's weights applied to every kv
-// head's values (32-bit, from the kernel above with v_rep = num_kv).  One thread per output element.
-template <typename T>
+// head's values (32-bit, from the kernel above with v_rep = num_kv).  One thread per (token, kv head, element)
+// reads its column of the parts once and finishes the GQ heads of that kv head together; the mixer lies in shared
+// memory.  GQ = 0: any group size, one head at a time.
+template <typename T, int GQ>
 __global__ void mix_heads_kernel(const float* __restrict__ part, const float* __restrict__ mix, T* __restrict__ out,
-                                 long long total, int num_q, int num_kv, int v_dim) {
+                                 long long total, int num_q, int num_kv, int v_dim, int in_smem) {
+  extern __shared__ float mix_smem[];  // [num_q][num_q], unless the mixer is too large for it
   pdl_launch_dependents();
   pdl_wait();
+  if (in_smem) {
+    for (int i = threadIdx.x; i < num_q * num_q; i += blockDim.x) mix_smem[i] = mix[i];
+    __syncthreads();
+  }
+  const float* mix_s = in_smem ? mix_smem : mix;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const int e = (int)(i % v_dim);
-  const long long th = i / v_dim;
-  const int h = (int)(th % num_q);
-  const long long t = th / num_q;
-  const int kh = h / (num_q / num_kv);
-  const float* p = part + ((t * num_q) * num_kv + kh) * v_dim + e;
-  float acc = 0.f;
-  for (int g = 0; g < num_q; ++g) acc += mix[h * num_q + g] * p[(long long)g * num_kv * v_dim];
-  out[i] = from_f32<T>(acc);
+  const long long tc = i / v_dim;
+  const int c = (int)(tc % num_kv);
+  const long long t = tc / num_kv;
+  const int gq = num_q / num_kv;
+  const float* p = part + ((t * num_q) * num_kv + c) * v_dim + e;
+  const long long step = (long long)num_kv * v_dim;
+  T* o = out + (t * num_q + (long long)c * gq) * v_dim + e;
+  if (GQ > 0) {
+    float acc[GQ > 0 ? GQ : 1];
+#pragma unroll
+    for (int j = 0; j < GQ; ++j) acc[j] = 0.f;
+    for (int g = 0; g < num_q; ++g) {
+      const float pv = p[g * step];
+#pragma unroll
+      for (int j = 0; j < GQ; ++j) acc[j] = fmaf(mix_s[(c * GQ + j) * num_q + g], pv, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < GQ; ++j) o[(long long)j * v_dim] = from_f32<T>(acc[j]);
+  } else {
+    for (int j = 0; j < gq; ++j) {
+      float acc = 0.f;
+      for (int g = 0; g < num_q; ++g) acc = fmaf(mix_s[(c * gq + j) * num_q + g], p[g * step], acc);
+      o[(long long)j * v_dim] = from_f32<T>(acc);
+    }
+  }
+}
+
+template <typename T>
+static int launch_mix(const float* parts, const float* mix, void* out, int tokens, int num_q, int num_kv, int v_dim,
+                      cudaStream_t st) {
+  const long long total = (long long)tokens * num_kv * v_dim;
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
+  const dim3 grid((int)blocks), block(256);
+  size_t smem = (size_t)num_q * num_q * sizeof(float);
+  const int in_smem = smem <= 40 * 1024;
+  if (!in_smem) smem = 0;
+#define MIX_GO(GQ)                                                                                                  \
+  return ullm_launch_kernel(mix_heads_kernel<T, GQ>, grid, block, smem, st, parts, mix, (T*)out, total, num_q, num_kv, \
+                            v_dim, in_smem)
+  switch (num_q / num_kv) {
+    case 1: MIX_GO(1);
+    case 2: MIX_GO(2);
+    case 4: MIX_GO(4);
+    case 8: MIX_GO(8);
+    default: MIX_GO(0);
+  }
+#undef MIX_GO
 }
 
 template <typename T>
@@ -217,19 +265,9 @@ extern "C" int ullm_mix_heads(int dtype, const float* parts, const float* mix, v
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || num_q <= 0 || num_kv <= 0 || v_dim <= 0 || num_q % num_kv) return ULLM_ERR_BAD_SIZE;
   if (tokens == 0) return ULLM_OK;
-  const long long total = (long long)tokens * num_q * v_dim;
-  const long long blocks = (total + 255) / 256;
-  if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
-  const dim3 grid((int)blocks), block(256);
-  if (dtype == ULLM_DTYPE_F32)
-    return ullm_launch_kernel(mix_heads_kernel<float>, grid, block, 0, st, parts, mix, (float*)out, total, num_q,
-                              num_kv, v_dim);
-  if (dtype == ULLM_DTYPE_BF16)
-    return ullm_launch_kernel(mix_heads_kernel<__nv_bfloat16>, grid, block, 0, st, parts, mix, (__nv_bfloat16*)out,
-                              total, num_q, num_kv, v_dim);
-  if (dtype == ULLM_DTYPE_F16)
-    return ullm_launch_kernel(mix_heads_kernel<__half>, grid, block, 0, st, parts, mix, (__half*)out, total, num_q,
-                              num_kv, v_dim);
+  if (dtype == ULLM_DTYPE_F32) return launch_mix<float>(parts, mix, out, tokens, num_q, num_kv, v_dim, st);
+  if (dtype == ULLM_DTYPE_BF16) return launch_mix<__nv_bfloat16>(parts, mix, out, tokens, num_q, num_kv, v_dim, st);
+  if (dtype == ULLM_DTYPE_F16) return launch_mix<__half>(parts, mix, out, tokens, num_q, num_kv, v_dim, st);
   return ULLM_ERR_BAD_DTYPE;
 }
 
