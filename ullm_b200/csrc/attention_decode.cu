@@ -718,7 +718,7 @@ extern "C" int ullm_decode_attention_fused(const void* qkv, long long q_row_stri
                                            float eps, const float* cos_t, const float* sin_t, int max_positions,
                                            const int* positions, const int* slot_mapping, int* status, void* stream) {
   if (cos_t == nullptr || sin_t == nullptr || positions == nullptr || max_positions <= 0) return ULLM_ERR_BAD_SIZE;
-  DecFuse fu;
+  DecFuse fu = {};  // (every field this entry does not set is off)
   fu.q_w = q_w;
   fu.k_w = k_w;
   fu.cos_t = cos_t;
