@@ -311,12 +311,16 @@ class CpuKernels:
         if copy is not None:
             copy.copy_(v.to(copy.dtype))
 
-    def norm_scale_add(self, a, stream, weight, eps, mult, copy=None):
+    def norm_scale_add(self, a, stream, weight, eps, mult, copy=None, next_norm=None):
         self._count("add_rmsnorm")
         x = a.float()
         stream += mult * (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight)
         if copy is not None:
             copy.copy_(stream.to(copy.dtype))
+        if next_norm is not None:
+            w2, eps2, out = next_norm
+            out.copy_((stream / torch.sqrt(stream.pow(2).mean(-1, keepdim=True) + eps2) * w2).to(out.dtype))
+            return True
 
     def rmsnorm_rows_f32(self, stream, rows, weight, eps, out):
         self._count("add_rmsnorm")

@@ -240,6 +240,7 @@ class Kernels:
             "ullm_act_mul_clamped": [I, P, P, I, I, F, F, P],
             "ullm_embed_scaled": [I, P, P, P, P, I, I, I, F, P, P, P, P, P, P, P],
             "ullm_norm_scale_add": [I, P, P, P, P, I, I, F, F, P],
+            "ullm_norm_scale_add_norm": [I, P, P, P, I, I, F, F, P, F, P, P],
             "ullm_rmsnorm_rows_f32": [I, P, P, P, P, I, I, I, F, P, P],
             "ullm_cast_rows_f32": [I, P, P, LL, P],
             "ullm_mlstm_recurrence": [I, P, LL, I, I, I, P, P, P, P, LL, P, P, P, P, I, I, I, I, F, F, I, P, P],
@@ -755,15 +756,29 @@ class Kernels:
                                                _stream()), "embed_scaled")
 
     @_timed("add_rmsnorm")
-    def norm_scale_add(self, a, stream, weight, eps: float, mult: float, copy=None):
+    def norm_scale_add(self, a, stream, weight, eps: float, mult: float, copy=None, next_norm=None):
         """stream (float32, in place) += mult * weight * a / sqrt(mean(a^2) + eps); `copy` (a's dtype, optional)
-        gets the rounded stream."""
+        gets the rounded stream.  `next_norm` = (weight2, eps2, out): the same kernel also leaves the RMSNorm of
+        the updated stream in `out` (a's dtype); False is returned when it does not take the row length (nothing
+        has run then)."""
         _need(a, "a")
         _need(stream, "stream", torch.float32)
         _need(weight, "weight", torch.float32)
         rows, cols = a.shape
         if stream.shape != a.shape or weight.numel() != cols:
             raise KernelError(f"norm_scale_add: a {tuple(a.shape)}, stream {tuple(stream.shape)}, weight {tuple(weight.shape)}")
+        if next_norm is not None:
+            w2, eps2, out = next_norm
+            if copy is not None or cols * 4 > 40 * 1024:
+                return False
+            _need(w2, "next norm weight", torch.float32)
+            _need(out, "out", a.dtype)
+            if out.shape != a.shape or w2.numel() != cols:
+                raise KernelError("norm_scale_add: the next norm's shapes differ")
+            self._check(self.lib.ullm_norm_scale_add_norm(_DT[a.dtype], _ptr(a), _ptr(stream), _ptr(weight), rows, cols,
+                                                          float(eps), float(mult), _ptr(w2), float(eps2), _ptr(out),
+                                                          _stream()), "norm_scale_add_norm")
+            return True
         if copy is not None:
             _need(copy, "copy", a.dtype)
             if copy.shape != a.shape:

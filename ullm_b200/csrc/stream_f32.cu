@@ -3,6 +3,7 @@
 //
 //   embed_scaled      stream[t] = table[id[t]] * scale (+ sinusoid of the position), copy[t] = round(stream[t])
 //   norm_scale_add    stream[t] += mult * w * a[t] / sqrt(mean(a[t]^2) + eps),       copy[t] = round(stream[t])
+//   norm_scale_add_norm   the same, and out[t] = the NEXT norm of the updated stream[t]
 //   rmsnorm_rows_f32  out[r] = round(w * s / sqrt(mean(s^2) + eps)), s = stream[rows[r]]
 //   cast_rows_f32     copy = round(stream)
 //   gated_add_f32     stream[t] += sigmoid(g1[t] + b1) * a[t] (+ sigmoid(g2[t] + b2) * f[t]),       copy[t] = round(stream[t])
@@ -67,6 +68,35 @@ __global__ void norm_scale_add_kernel(const T* __restrict__ a, float* __restrict
     stream[base + c] = s;
     if (copy != nullptr) copy[base + c] = from_f32<T>(s);
   }
+}
+
+// The same, and in the same pass the NEXT norm of the updated stream: out[t] = round(w2 * s / sqrt(mean(s^2) + eps2))
+// for s = the stream's new row, which waits in shared memory (`cols` floats) between the two sums: the stream is
+// neither written and read again nor normed by a kernel of its own.
+template <typename T>
+__global__ void norm_scale_add_norm_kernel(const T* __restrict__ a, float* __restrict__ stream,
+                                           const float* __restrict__ w, int cols, float eps, float mult,
+                                           const float* __restrict__ w2, float eps2, T* __restrict__ out) {
+  extern __shared__ float row_s[];
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long base = (long long)blockIdx.x * cols;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = to_f32(a[base + c]);
+    acc += v * v;
+  }
+  const float rstd = 1.f / sqrtf(block_sum(acc, scratch) / (float)cols + eps);
+  float acc2 = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float s = stream[base + c] + mult * (to_f32(a[base + c]) * rstd * w[c]);
+    stream[base + c] = s;
+    row_s[c] = s;
+    acc2 += s * s;
+  }
+  const float rstd2 = 1.f / sqrtf(block_sum(acc2, scratch) / (float)cols + eps2);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) out[base + c] = from_f32<T>(row_s[c] * rstd2 * w2[c]);
 }
 
 template <typename T>
@@ -206,6 +236,28 @@ extern "C" int ullm_norm_scale_add(int dtype, const void* a, float* stream, cons
   if (dtype == ULLM_DTYPE_F16)
     return ullm_launch_kernel(norm_scale_add_kernel<__half>, grid, block, 0, st, (const __half*)a, stream, w,
                               (__half*)copy, cols, eps, mult);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// stream += mult * w * a / rms(a), and out = the next norm (w2, eps2) of the updated stream, in one kernel.
+extern "C" int ullm_norm_scale_add_norm(int dtype, const void* a, float* stream, const float* w, int rows, int cols,
+                                        float eps, float mult, const float* w2, float eps2, void* out,
+                                        void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (rows < 0 || cols <= 0) return ULLM_ERR_BAD_SIZE;
+  if ((size_t)cols * sizeof(float) > 40 * 1024) return ULLM_ERR_UNSUPPORTED;
+  if (rows == 0) return ULLM_OK;
+  const dim3 grid(rows), block(row_threads(cols));
+  const size_t smem = (size_t)cols * sizeof(float);
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(norm_scale_add_norm_kernel<float>, grid, block, smem, st, (const float*)a, stream, w,
+                              cols, eps, mult, w2, eps2, (float*)out);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(norm_scale_add_norm_kernel<__nv_bfloat16>, grid, block, smem, st,
+                              (const __nv_bfloat16*)a, stream, w, cols, eps, mult, w2, eps2, (__nv_bfloat16*)out);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(norm_scale_add_norm_kernel<__half>, grid, block, smem, st, (const __half*)a, stream, w,
+                              cols, eps, mult, w2, eps2, (__half*)out);
   return ULLM_ERR_BAD_DTYPE;
 }
 

@@ -104,6 +104,9 @@ class StepContext:
     # a 32-bit residual stream rounded to the engine's dtype (the stream itself under a 32-bit engine): what the
     # next sub-layer's matrix products read; whoever updates the stream leaves it here
     stream_operand: object = None
+    # (norm object, its rows of the stream as it stands) left by a block whose last kernel also applied the next
+    # block's first norm
+    prepared_norm: object = None
     token_side: object = None  # the model's per-layer token input table (parts.embedding.TokenSideTable), if any
     shared: dict = field(default_factory=dict)  # what an execution leaves for later executions of the same step
     sum_kv_len: int = 0  # tokens all requests of the step hold after it, padding rows not counted

@@ -285,8 +285,16 @@ class ParallelGatedBlock(Block):
         # the normed rows, the stream's copy, both sub-layers at once, the gates in 32-bit, the side input
         return 2 * W + self.mixer.activation_elems() + ff + 4 * W + 2 * self.side_dim + W
 
-    def forward(self, x, residual, ctx, cache):
-        """The stream arrives as `x` (first block, residual None) or as `residual` (x None); returns (None, stream)."""
+    takes_next_norm = True  # `forward` accepts the norm that the next block will apply first
+
+    def accepts_folded_norm(self) -> bool:
+        """True: this block can start from normed rows that the block before left in `ctx.prepared_norm`."""
+        return self.mixer_norm.rms_params() is not None
+
+    def forward(self, x, residual, ctx, cache, next_norm=None):
+        """The stream arrives as `x` (first block, residual None) or as `residual` (x None); returns (None, stream).
+        `next_norm`: the norm the next block applies first; with a token side input the kernel that adds it to the
+        stream also leaves that norm's rows (`ctx.prepared_norm`), which a block of this kind then starts from."""
         K = kernels()
         stream = residual if residual is not None else x
         if stream.dtype != torch.float32:
@@ -294,8 +302,12 @@ class ParallelGatedBlock(Block):
         T, W = stream.shape
         n, ws = self.names, ctx.workspace
         dt = self.mixer.operand_dtype()
-        h = ws.tokens("block.normed", T, W, dt)
-        self.mixer_norm.forward_rows(stream, None, h)
+        prepared, ctx.prepared_norm = getattr(ctx, "prepared_norm", None), None
+        if prepared is not None and prepared[0] is self.mixer_norm and prepared[1].shape == (T, W):
+            h = prepared[1]
+        else:
+            h = ws.tokens("block.normed", T, W, dt)
+            self.mixer_norm.forward_rows(stream, None, h)
         a = self.mixer.forward(h, ctx, cache)
         f = self.feed_forward.forward(h, ctx) if self.feed_forward is not None else None
         copy = ws.tokens("model.stream_copy", T, W, dt) if (self.side_dim and dt != torch.float32) else None
@@ -316,6 +328,16 @@ class ParallelGatedBlock(Block):
                             ctx.token_req if last is not None else None, ctx.req_slots if last is not None else None)
             y = ws.tokens("block.side_out", T, W, dt)
             linear(g, self.tensors[n["side_proj"]], y)
-            K.norm_scale_add(y, stream, self.tensors[n["side_norm"]], self.eps, 1.0, None)
+            nxt = next_norm.rms_params() if next_norm is not None else None
+            done = False
+            if nxt is not None and nxt[0].numel() == W:
+                # (all of this block's readers of h are done: the next block's rows take its place)
+                h_next = ws.tokens("block.normed", T, W, dt)
+                done = K.norm_scale_add(y, stream, self.tensors[n["side_norm"]], self.eps, 1.0, None,
+                                        next_norm=(nxt[0], nxt[1], h_next))
+                if done:
+                    ctx.prepared_norm = (next_norm, h_next)
+            if not done:
+                K.norm_scale_add(y, stream, self.tensors[n["side_norm"]], self.eps, 1.0, None)
         ctx.stream_operand = None
         return None, stream

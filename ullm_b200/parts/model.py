@@ -119,6 +119,7 @@ class DecoderModel(Part):
             else:
                 x, residual = block.forward(x, residual, ctx, caches[i])
         ctx.folded_norm = None
+        ctx.prepared_norm = None
         return x, residual
 
     def forward(self, ctx, caches):
