@@ -685,10 +685,10 @@ def borosun_config(width: int, heads: int, kv_heads: int, ff: int, window: int, 
     """`groups` times four layers: causal attention (convolved, mixed heads), windowed attention (capped), and two
     state layers, every one with a dense feed-forward."""
     att = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, conv=4, scale=128 ** -0.5, v_mix=True,
-               rot=dict(dims=128, base=500000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
-    win = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=0.08, softcap=30.0, v_mix=True,
-               mask=dict(size=window), rot=dict(dims=64, base=500000.0))
-    st = dict(heads=state_heads, dim=state_dim, vdim=state_vdim, tau=16.0, decay_rank=16)
+               rot=dict(dims=128, base=1e6, scaling=dict(factor=4.0, low=1.0, high=8.0, original=8192)))
+    win = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=0.08, softcap=50.0, v_mix=True,
+               mask=dict(size=window), rot=dict(dims=64, base=1e6))
+    st = dict(heads=state_heads, dim=state_dim, vdim=state_vdim, tau=8.0, decay_rank=32)
     mlp = dict(kind="dense", ff=ff)
     layers = []
     for _ in range(groups):
