@@ -208,7 +208,7 @@ def one_key_window_model(size, dtype, dim=16, vdim=24, cap=None):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("size", [1, 8, 16, 5, 17])
-@pytest.mark.parametrize("dim,vdim", [(16, 24), (64, 64)])
+@pytest.mark.parametrize("dim,vdim", [(16, 24), (64, 64), (128, 128)])  # the last two: tensor-core kernels in bfloat16
 def test_window_edges_in_prompts_and_decoding(tmp_path, dtype, size, dim, vdim):
     page = 8
     cfg, w = one_key_window_model(size, dtype, dim, vdim)
@@ -251,6 +251,24 @@ def test_score_cap_decides(tmp_path, dtype, dim, vdim):
     r = make_runner(tmp_path, cfg, w, 8, dtype, num_pages=12)
     got = replay(r, {"a": ids}, [[("a", 30)], [("a", 2)]] + [[("a", 1)] for _ in range(18)])["a"]
     assert_close(got, ref, dtype, "capped scores")
+
+
+@pytest.mark.parametrize("dim", [64, 128])
+def test_scores_deep_inside_the_cap_on_the_tensor_cores(tmp_path, dim):
+    """bfloat16, head sizes of the tensor-core kernels, |score| at most a sixth of the cap: the prompt kernel's
+    short form of the cap must agree with the plain model as its exact form does (prompt portions and decoding)."""
+    from ullm_b200.csrc import kernels
+
+    cfg = config(64, 83, [("attention_2", attention_2(4, 2, dim, dim, 1.3 / dim, 50, rot(dim // 2, 1e4), softcap=8.0), dense(48))])
+    w = cast(pb.random_weights(cfg, seed=dim), "bfloat16")
+    ids = random_ids(cfg["vocab"], 120, 6)
+    r = make_runner(tmp_path, cfg, w, 16, "bfloat16", num_pages=12)
+    got = replay(r, {"a": ids}, [[("a", 70)], [("a", 3)], [("a", 40)]] + [[("a", 1)] for _ in range(7)])["a"]
+    assert_rows_close(got, oracle(ids, w, cfg), "bfloat16", "cap in its linear regime")
+    if device() != "cpu":
+        r2 = make_runner(tmp_path, cfg, w, 16, "bfloat16", num_pages=12, name="p")
+        replay(r2, {"b": ids}, [[("b", 120)]])
+        assert kernels().attention_path == ("prefill" if dim == 64 else "prefill_tcgen05")
 
 
 def far_key_model(dtype):

@@ -210,9 +210,14 @@ struct TpParams {
   int* status;
   int max_pages, num_requests, num_q, num_kv, page_size, window;
   float scale_log2;
+  float cap_pre;  // capped scores (CAP): s <- cap * tanh(s * scale / cap); scale / cap here, scale_log2 = cap * log2(e)
   long long num_pages;
 };
 
+// tanh by one exponential and one division of the hardware's units: 1 - 2 / (e^(2x) + 1)
+__device__ __forceinline__ float tp_tanh(float x) { return 1.f - __fdividef(2.f, tp_ex2(x * 2.8853900817779268f) + 1.f); }
+
+template <bool CAP>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v, const TpParams p) {
@@ -489,6 +494,28 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
 #pragma unroll
       for (int c = 0; c < TP_KEYS / 32; ++c) tp_tmem_ld32_nowait(tmem_s + c * 32, sr + c * 32);
       tp_tmem_ld_wait();
+      if (CAP) {
+        // Where every score of the warp's rows lies deep inside the cap (|s scale / cap| <= 1/4: the regime caps
+        // are chosen for), tanh is its series through x^7 (next term 62 x^9 / 2835 < 1e-7 there) on the
+        // multiply-add pipe; otherwise the exact form, two operations of the special-function unit per score.
+        float big = 0.f;
+#pragma unroll
+        for (int k = 0; k < TP_KEYS; ++k) {
+          const float x = __uint_as_float(sr[k]) * p.cap_pre;
+          big = fmaxf(big, fabsf(x));
+          sr[k] = __float_as_uint(x);
+        }
+        if (__all_sync(0xffffffffu, big <= 0.25f)) {
+#pragma unroll
+          for (int k = 0; k < TP_KEYS; ++k) {
+            const float x = __uint_as_float(sr[k]), y = x * x;
+            sr[k] = __float_as_uint(x * fmaf(y, fmaf(y, fmaf(y, -17.f / 315.f, 2.f / 15.f), -1.f / 3.f), 1.f));
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < TP_KEYS; ++k) sr[k] = __float_as_uint(tp_tanh(__uint_as_float(sr[k])));
+        }
+      }
       const bool need_mask = rows_valid < TP_ROWS || key0 + TP_KEYS - 1 > pf || (p.window > 0 && key0 < pl - p.window + 1);
       if (need_mask) {
 #pragma unroll
@@ -648,14 +675,14 @@ extern "C" int ullm_prefill_attention_pair_supported(int head_dim, int num_q, in
   return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }
 
-static int g_tp_attr_set = 0;
-extern "C" int ullm_prefill_attention_pair(const void* q, long long q_row_stride, void* out, const void* k_cache,
-                                           const void* v_cache, const int* block_table, int max_pages,
-                                           const int* req_slots, const int* cu_q, const int* kv_len, int tokens,
-                                           int num_requests, int num_q, int num_kv, int head_dim, int page_size,
-                                           int window, float scale, long long num_pages, int* status, void* stream) {
+template <bool CAP>
+static int tp_launch(const void* q, long long q_row_stride, void* out, const void* k_cache, const void* v_cache,
+                     const int* block_table, int max_pages, const int* req_slots, const int* cu_q, const int* kv_len,
+                     int tokens, int num_requests, int num_q, int num_kv, int head_dim, int page_size, int window,
+                     float scale, long long num_pages, int* status, void* stream, float softcap) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || num_requests <= 0 || max_pages <= 0 || window < 0) return ULLM_ERR_BAD_SIZE;
+  if (CAP && !(softcap > 0.f)) return ULLM_ERR_BAD_SIZE;
   if (!ullm_prefill_attention_pair_supported(head_dim, num_q, num_kv, page_size)) return ULLM_ERR_UNSUPPORTED;
   if (q_row_stride % 8 || ((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16)
     return ULLM_ERR_UNSUPPORTED;
@@ -667,13 +694,15 @@ extern "C" int ullm_prefill_attention_pair(const void* q, long long q_row_stride
       !ullm_tma_map_kv(k_cache, num_pages, page_size, num_kv, TP_D, page_size, &mk) ||
       !ullm_tma_map_kv(v_cache, num_pages, page_size, num_kv, TP_D, page_size, &mv))
     return ULLM_ERR_LAUNCH;
-  if (!g_tp_attr_set) {
-    if (cudaFuncSetAttribute(prefill_attention_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) !=
-        cudaSuccess)
+  static int attr_set = 0;  // (one flag per instantiation)
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(prefill_attention_pair_kernel<CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             TP_SMEM) != cudaSuccess)
       return ULLM_ERR_LAUNCH;
-    g_tp_attr_set = 1;
+    attr_set = 1;
   }
-  TpParams p;
+  const float log2e = 1.4426950408889634f;
+  TpParams p = {};
   p.block_table = block_table;
   p.req_slots = req_slots;
   p.cu_q = cu_q;
@@ -686,9 +715,33 @@ extern "C" int ullm_prefill_attention_pair(const void* q, long long q_row_stride
   p.num_kv = num_kv;
   p.page_size = page_size;
   p.window = window;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale_log2 = CAP ? softcap * log2e : scale * log2e;
+  p.cap_pre = CAP ? scale / softcap : 0.f;
   p.num_pages = num_pages;
   const int tpb = 2 * (TP_ROWS / G);
   dim3 grid(((tokens + tpb - 1) / tpb + num_requests) * num_kv);
-  return ullm_launch_kernel(prefill_attention_pair_kernel, grid, dim3(TP_THREADS), (size_t)TP_SMEM, st, mq, mk, mv, p);
+  return ullm_launch_kernel(prefill_attention_pair_kernel<CAP>, grid, dim3(TP_THREADS), (size_t)TP_SMEM, st, mq, mk,
+                            mv, p);
+}
+
+extern "C" int ullm_prefill_attention_pair(const void* q, long long q_row_stride, void* out, const void* k_cache,
+                                           const void* v_cache, const int* block_table, int max_pages,
+                                           const int* req_slots, const int* cu_q, const int* kv_len, int tokens,
+                                           int num_requests, int num_q, int num_kv, int head_dim, int page_size,
+                                           int window, float scale, long long num_pages, int* status, void* stream) {
+  return tp_launch<false>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
+                          tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status,
+                          stream, 0.f);
+}
+
+// With capped scores, s <- softcap * tanh(s * scale / softcap).
+extern "C" int ullm_prefill_attention_pair_capped(const void* q, long long q_row_stride, void* out,
+                                                  const void* k_cache, const void* v_cache, const int* block_table,
+                                                  int max_pages, const int* req_slots, const int* cu_q,
+                                                  const int* kv_len, int tokens, int num_requests, int num_q,
+                                                  int num_kv, int head_dim, int page_size, int window, float scale,
+                                                  long long num_pages, int* status, void* stream, float softcap) {
+  return tp_launch<true>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
+                         tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status,
+                         stream, softcap);
 }
