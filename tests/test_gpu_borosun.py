@@ -271,21 +271,23 @@ def test_scores_deep_inside_the_cap_on_the_tensor_cores(tmp_path, dim):
         assert kernels().attention_path == ("prefill" if dim == 64 else "prefill_tcgen05")
 
 
-def far_key_model(dtype):
+def far_key_model(dtype, dim=16, vdim=12):
     """One causal layer (convolution, mixed heads, two kv heads) with a large scale, without feed-forward."""
-    cfg = config(48, 61, [("attention", attention(4, 2, 16, 12, 1.1 if dtype == "float32" else 0.7,
-                                                 rot(8, 50.0, (4.0, 1.0, 2.0, 16)), conv=3), None)])
+    scale = (1.1 if dtype == "float32" else 0.7) * (16 / dim) ** 0.5
+    cfg = config(48, 61, [("attention", attention(4, 2, dim, vdim, scale, rot(8, 50.0, (4.0, 1.0, 2.0, 16)), conv=3), None)])
     w = pb.random_weights(cfg, seed=5)
     w["l0.mix.talk"] = torch.tensor([[0.2, 0.9, -0.4, 0.3], [0.0, 1.0, 0.0, 0.0], [0.5, 0.1, 0.6, -0.2],
                                      [-0.3, 0.2, 0.8, 0.3]])
+    w["l0.mix.o"] = w["l0.mix.o"] * 2.5  # (the mixer's share of the stream beside the embedding)
     return cfg, cast(w, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_far_keys_and_mixed_heads_over_two_kv_heads(tmp_path, dtype):
+@pytest.mark.parametrize("dim,vdim", [(16, 12), (64, 64), (128, 128)])  # the last two: tensor-core kernels in bfloat16
+def test_far_keys_and_mixed_heads_over_two_kv_heads(tmp_path, dtype, dim, vdim):
     """A causal layer over 300 tokens and many pages: the first tokens stay visible to the end, and the head
     mixer is no symmetric matrix, so its transpose, or a head that reads the other kv head's values, shows."""
-    cfg, w = far_key_model(dtype)
+    cfg, w = far_key_model(dtype, dim, vdim)
     n = 300
     # the test has power: the token at position 2 decides logits among the last twenty, three hundred keys later
     # (the first of a few token sequences for which it does), and so does the mixer's orientation

@@ -212,12 +212,15 @@ struct TpParams {
   float scale_log2;
   float cap_pre;  // capped scores (CAP): s <- cap * tanh(s * scale / cap); scale / cap here, scale_log2 = cap * log2(e)
   long long num_pages;
+  // PARTS: the grid counts (token block, key head, VALUE head); the weights of the key head's query heads meet the
+  // values of any kv head, and the 32-bit results go here, [token][head][value head][128] (`out` is not written)
+  float* parts;
 };
 
 // tanh by one exponential and one division of the hardware's units: 1 - 2 / (e^(2x) + 1)
 __device__ __forceinline__ float tp_tanh(float x) { return 1.f - __fdividef(2.f, tp_ex2(x * 2.8853900817779268f) + 1.f); }
 
-template <bool CAP>
+template <bool CAP, bool PARTS>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v, const TpParams p) {
@@ -244,14 +247,16 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // A 1-D grid, numbered so that consecutive blocks are the same token block of all kv heads: the block
   // scheduler then starts the heaviest blocks of EVERY head first (longest work first keeps the SMs level).
-  const int kh = (int)(blockIdx.x % p.num_kv);
+  const int pairs = PARTS ? p.num_kv * p.num_kv : p.num_kv;
+  const int kh = PARTS ? (int)(blockIdx.x % pairs) / p.num_kv : (int)(blockIdx.x % p.num_kv);  // key head
+  const int vh = PARTS ? (int)(blockIdx.x % pairs) % p.num_kv : kh;                            // value head
   const int G = p.num_q / p.num_kv;
   const int tpt = TP_ROWS / G;  // tokens of a query tile
   const int tpb = 2 * tpt;      // tokens of a block
   pdl_wait();
 
   // ---- which request and which of its token blocks (numbered from the back: heavy blocks first) ---------
-  const int block_id = (int)(gridDim.x / p.num_kv) - 1 - (int)(blockIdx.x / p.num_kv);
+  const int block_id = (int)(gridDim.x / pairs) - 1 - (int)(blockIdx.x / pairs);
   int r = -1, first = 0, q_len = 0, q_begin = 0;
   {
     int running = 0;
@@ -276,7 +281,9 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
   if (kvl <= 0 || p0 < 0) {
     for (int i = tid; i < ntok_all * G * TP_D; i += blockDim.x) {
       const int row = i / TP_D, d = i - row * TP_D;
-      p.out[((long long)(q_begin + first + row / G) * p.num_q + kh * G + row % G) * TP_D + d] = __float2bfloat16_rn(0.f);
+      const long long th = (long long)(q_begin + first + row / G) * p.num_q + kh * G + row % G;
+      if (PARTS) p.parts[(th * p.num_kv + vh) * TP_D + d] = 0.f;
+      else p.out[th * TP_D + d] = __float2bfloat16_rn(0.f);
     }
     return;
   }
@@ -348,8 +355,9 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
       if (lane < pages_per_tile) {
         const int pcoord = page >= 0 ? page : (int)p.num_pages;
         unsigned char* d = dst + lane * p.page_size * 128;
-        tp_tma_4d(d, map, bar, 0, kh, 0, pcoord);
-        tp_tma_4d(d + TP_TILE_KV / 2, map, bar, 64, kh, 0, pcoord);
+        const int head = (PARTS && map == &map_v) ? vh : kh;
+        tp_tma_4d(d, map, bar, 0, head, 0, pcoord);
+        tp_tma_4d(d + TP_TILE_KV / 2, map, bar, 64, head, 0, pcoord);
       }
     };
     if (lane == 0) tp_mbar_expect_tx(&k0_full, TP_TILE_KV);
@@ -594,13 +602,23 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap map_q, const _
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* op = p.out + ((long long)(q_begin + first + i * tpt + row / G) * p.num_q + kh * G + row % G) * TP_D;
+      const long long th = (long long)(q_begin + first + i * tpt + row / G) * p.num_q + kh * G + row % G;
+      __nv_bfloat16* op = p.out + th * TP_D;
+      float* pp = PARTS ? p.parts + (th * p.num_kv + vh) * TP_D : nullptr;
 #pragma unroll
       for (int c = 0; c < TP_D / 32; ++c) {
         uint32_t v[32];
         tp_tmem_ld32_nowait(tmem_o + c * 32, v);  // all lanes of the warp take part
         tp_tmem_ld_wait();
-        if (row_ok && ok) {
+        if (PARTS) {
+          if (row_ok && ok) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(pp + c * 32 + q * 4) =
+                  make_float4(__uint_as_float(v[q * 4 + 0]) * inv, __uint_as_float(v[q * 4 + 1]) * inv,
+                              __uint_as_float(v[q * 4 + 2]) * inv, __uint_as_float(v[q * 4 + 3]) * inv);
+          }
+        } else if (row_ok && ok) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 chunk;
@@ -675,16 +693,17 @@ extern "C" int ullm_prefill_attention_pair_supported(int head_dim, int num_q, in
   return page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128;
 }
 
-template <bool CAP>
+template <bool CAP, bool PARTS>
 static int tp_launch(const void* q, long long q_row_stride, void* out, const void* k_cache, const void* v_cache,
                      const int* block_table, int max_pages, const int* req_slots, const int* cu_q, const int* kv_len,
                      int tokens, int num_requests, int num_q, int num_kv, int head_dim, int page_size, int window,
-                     float scale, long long num_pages, int* status, void* stream, float softcap) {
+                     float scale, long long num_pages, int* status, void* stream, float softcap, float* parts) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || num_requests <= 0 || max_pages <= 0 || window < 0) return ULLM_ERR_BAD_SIZE;
   if (CAP && !(softcap > 0.f)) return ULLM_ERR_BAD_SIZE;
+  if (PARTS && (parts == nullptr || ((uintptr_t)parts) % 16)) return ULLM_ERR_BAD_SIZE;
   if (!ullm_prefill_attention_pair_supported(head_dim, num_q, num_kv, page_size)) return ULLM_ERR_UNSUPPORTED;
-  if (q_row_stride % 8 || ((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % 16)
+  if (q_row_stride % 8 || ((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (PARTS ? 0 : (uintptr_t)out)) % 16)
     return ULLM_ERR_UNSUPPORTED;
   if (q_row_stride % TP_D) return ULLM_ERR_UNSUPPORTED;
   if (tokens == 0) return ULLM_OK;
@@ -696,7 +715,7 @@ static int tp_launch(const void* q, long long q_row_stride, void* out, const voi
     return ULLM_ERR_LAUNCH;
   static int attr_set = 0;  // (one flag per instantiation)
   if (!attr_set) {
-    if (cudaFuncSetAttribute(prefill_attention_pair_kernel<CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(prefill_attention_pair_kernel<CAP, PARTS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              TP_SMEM) != cudaSuccess)
       return ULLM_ERR_LAUNCH;
     attr_set = 1;
@@ -718,9 +737,10 @@ static int tp_launch(const void* q, long long q_row_stride, void* out, const voi
   p.scale_log2 = CAP ? softcap * log2e : scale * log2e;
   p.cap_pre = CAP ? scale / softcap : 0.f;
   p.num_pages = num_pages;
+  p.parts = PARTS ? parts : nullptr;
   const int tpb = 2 * (TP_ROWS / G);
-  dim3 grid(((tokens + tpb - 1) / tpb + num_requests) * num_kv);
-  return ullm_launch_kernel(prefill_attention_pair_kernel<CAP>, grid, dim3(TP_THREADS), (size_t)TP_SMEM, st, mq, mk,
+  dim3 grid(((tokens + tpb - 1) / tpb + num_requests) * num_kv * (PARTS ? num_kv : 1));
+  return ullm_launch_kernel(prefill_attention_pair_kernel<CAP, PARTS>, grid, dim3(TP_THREADS), (size_t)TP_SMEM, st, mq, mk,
                             mv, p);
 }
 
@@ -729,9 +749,9 @@ extern "C" int ullm_prefill_attention_pair(const void* q, long long q_row_stride
                                            const int* req_slots, const int* cu_q, const int* kv_len, int tokens,
                                            int num_requests, int num_q, int num_kv, int head_dim, int page_size,
                                            int window, float scale, long long num_pages, int* status, void* stream) {
-  return tp_launch<false>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
-                          tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status,
-                          stream, 0.f);
+  return tp_launch<false, false>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                 kv_len, tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale,
+                                 num_pages, status, stream, 0.f, nullptr);
 }
 
 // With capped scores, s <- softcap * tanh(s * scale / softcap).
@@ -741,7 +761,20 @@ extern "C" int ullm_prefill_attention_pair_capped(const void* q, long long q_row
                                                   const int* kv_len, int tokens, int num_requests, int num_q,
                                                   int num_kv, int head_dim, int page_size, int window, float scale,
                                                   long long num_pages, int* status, void* stream, float softcap) {
-  return tp_launch<true>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q, kv_len,
-                         tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status,
-                         stream, softcap);
+  return tp_launch<true, false>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                kv_len, tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale,
+                                num_pages, status, stream, softcap, nullptr);
+}
+
+// Every head's softmax weights applied to EVERY kv head's values, unrounded, into `parts` (32-bit,
+// [tokens][heads][kv heads][128]) for `ullm_mix_heads`.
+extern "C" int ullm_prefill_attention_pair_parts(const void* q, long long q_row_stride, float* parts,
+                                                 const void* k_cache, const void* v_cache, const int* block_table,
+                                                 int max_pages, const int* req_slots, const int* cu_q,
+                                                 const int* kv_len, int tokens, int num_requests, int num_q,
+                                                 int num_kv, int head_dim, int page_size, int window, float scale,
+                                                 long long num_pages, int* status, void* stream) {
+  return tp_launch<false, true>(q, q_row_stride, nullptr, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                kv_len, tokens, num_requests, num_q, num_kv, head_dim, page_size, window, scale,
+                                num_pages, status, stream, 0.f, parts);
 }

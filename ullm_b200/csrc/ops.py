@@ -228,6 +228,7 @@ class Kernels:
             "ullm_prefill_attention_tcgen05": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_pair": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_prefill_attention_pair_capped": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P, F],
+            "ullm_prefill_attention_pair_parts": [P, LL, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, LL, P, P],
             "ullm_linear_tcgen05": [P, P, P, P, I, I, I, I, I, P, LL, P, I, P, P],
             "ullm_linear_skinny": [P, P, P, P, I, I, I, I, I, P],
             "ullm_linear_stream": [P, P, P, P, P, I, I, I, I, I, P, P],
@@ -1335,14 +1336,18 @@ class Kernels:
                 self._decode_rows(qkv, out, k_pages, v_pages, block_table, req_slots, kv_len, num_q, num_kv, head_dim,
                                   page_size, window, scale, num_pages, False, ctx, None, keep_first, softcap, parts)
                 return
-            if (tc and parts is None and keep_first == 0 and self.use_tcgen05_attention
+            if (tc and keep_first == 0 and self.use_tcgen05_attention
                     and self.tc_attention_mode != "single" and qkv.stride(0) % head_dim == 0
                     and self.lib.ullm_prefill_attention_pair_supported(head_dim, num_q, num_kv, page_size)):
-                # head size 128: the tcgen05 prompt kernel with two query tiles per block, with or without the cap
-                args = (_ptr(qkv), qkv.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
-                        block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, ctx.num_requests, num_q,
-                        num_kv, head_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream())
-                if softcap > 0:
+                # head size 128: the tcgen05 prompt kernel with two query tiles per block, with or without the cap,
+                # or with every head's weights on every kv head's values
+                args = (_ptr(qkv), qkv.stride(0), _ptr(parts if parts is not None else out), _ptr(k_pages), _ptr(v_pages),
+                        _ptr(block_table), block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T,
+                        ctx.num_requests, num_q, num_kv, head_dim, page_size, int(window), float(scale), num_pages,
+                        _ptr(self.status), _stream())
+                if parts is not None:
+                    code = self.lib.ullm_prefill_attention_pair_parts(*args)
+                elif softcap > 0:
                     code = self.lib.ullm_prefill_attention_pair_capped(*args, float(softcap))
                 else:
                     code = self.lib.ullm_prefill_attention_pair(*args)
