@@ -146,3 +146,31 @@ def test_plain_convolution_reads_only_the_past():
     y = pb.short_conv(u, w)
     assert torch.equal(y[:, 1], u[:, 1])  # a filter that keeps the present tap only
     assert y[0, 0] == 100 * u[0, 0] and y[2, 0] == u[0, 0] + 10 * u[1, 0] + 100 * u[2, 0]
+
+
+def test_random_model_folder_round_trip(tmp_path):
+    """`random-model` writes a folder from the configuration alone; reading it back finds every size again,
+    the decay projection's inner size from the tensor it wrote."""
+    import json
+
+    from ullm_b200.config import load_model_spec
+    from ullm_b200.engine.cli import main
+    from ullm_b200.parts.model import DecoderModel
+    from ullm_b200.weights.safetensors_io import open_model_files
+
+    cfg = copy.deepcopy(CFG_B)
+    cfg["layers"][3]["mixer"]["decay_rank"] = 7
+    path = tmp_path / "cfg.json"
+    path.write_text(json.dumps(cfg))
+    out = str(tmp_path / "model")
+    assert main(["random-model", "--out", out, "--config", str(path), "--seed", "3", "--dtype", "bfloat16"]) == 0
+    files = open_model_files(out)
+    shapes = {n: tuple(f.shape(n)) for f in files for n in f.names()}
+    for f in files:
+        f.close()
+    assert shapes == pb.tensor_shapes(cfg)
+    assert shapes["l3.mix.a1"] == (7, cfg["width"])
+    del cfg["layers"][3]["mixer"]["decay_rank"]  # a folder made elsewhere does not carry the key
+    (tmp_path / "model" / "config.json").write_text(json.dumps(cfg))
+    _, spec = load_model_spec(out)
+    assert {n: tuple(d.shape) for n, d in DecoderModel(spec).all_decls().items()} == shapes
