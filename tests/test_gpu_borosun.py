@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_borosun as pb
-from borosun_helpers import (CONFIGS, attention, attention_2, config, dense, gla, make_runner, oracle, replay, rot,
+from borosun_helpers import (attention, attention_2, config, dense, gla, make_runner, oracle, replay, rot,
                              weights_for, write_model)
 from conftest import device
 from helpers import TOL, assert_close, errors, random_ids
