@@ -127,6 +127,17 @@ def test_parallel_gated_block_alone(tmp_path, dtype, tag, layer):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_convolution_longer_than_the_steps(tmp_path, dtype):
+    """Eleven taps: the memory outlives several steps of one to three tokens, and a first step is shorter than it."""
+    cfg = config(48, 61, [("attention", attention(4, 2, 16, 12, 0.25, rot(8, 50.0), conv=11, v_mix=True), dense(32))], side=8)
+    w = cast(pb.random_weights(cfg, seed=1), dtype)
+    ids = random_ids(61, 60, 3)
+    r = make_runner(tmp_path, cfg, w, 8, dtype)
+    plan = [[("a", 3)], [("a", 1)], [("a", 2)], [("a", 30)], [("a", 5)]] + [[("a", 1)] for _ in range(19)]
+    assert_rows_close(replay(r, {"a": ids}, plan)["a"], oracle(ids, w, cfg), dtype, "eleven taps")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_capped_logits_of_the_tied_head(tmp_path, dtype):
     """A (cap 9) against the same weights without a cap: the engine follows the configuration, and the cap matters."""
     cfg, w, page = weights_for("A", dtype)

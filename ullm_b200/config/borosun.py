@@ -135,8 +135,8 @@ class BorosunConfig:
                     raise BorosunConfigError(f"config.json: {where}.mixer.heads is no multiple of kv_heads")
                 _need(mix, "scale", where + ".mixer")
                 _check_rotation(mix, where + ".mixer")
-                if mix.get("conv") is not None and not 1 <= _positive_int(mix, "conv", where + ".mixer") <= 8:
-                    raise BorosunConfigError(f"config.json: {where}.mixer.conv must be 1 to 8 taps")
+                if mix.get("conv") is not None and not 1 <= _positive_int(mix, "conv", where + ".mixer") <= 32:
+                    raise BorosunConfigError(f"config.json: {where}.mixer.conv must be 1 to 32 taps")
                 if mix.get("softcap") is not None:
                     _positive(mix, "softcap", where + ".mixer")
                 if L["type"] == "attention_2":

@@ -21,7 +21,7 @@
 
 #define PREP_MAX_DIM 512
 #define PREP_WARPS 4
-#define PREP_MAX_TAPS 8
+#define PREP_MAX_TAPS 32
 
 template <typename T>
 __global__ void qkv_prepare_kernel(const T* __restrict__ qkv, long long row_stride, int tokens, int num_q, int num_kv,

@@ -89,8 +89,8 @@ class PagedAttention(Mixer):
         self.value_mix = value_mix
         self.unit_norm_after_rotation = bool(unit_norm_after_rotation)
         self.norm_eps = float(norm_eps)
-        if self.conv_taps < 0 or self.conv_taps > 8:
-            raise ValueError(f"conv_taps={conv_taps}: the convolution kernel takes 1 to 8 taps (0: none)")
+        if self.conv_taps < 0 or self.conv_taps > 32:
+            raise ValueError(f"conv_taps={conv_taps}: the convolution kernel takes 1 to 32 taps (0: none)")
         if self.score_cap is not None and self.score_cap <= 0:
             raise ValueError("score_cap must be positive")
         if value_mix not in (None, "first", "mix"):
