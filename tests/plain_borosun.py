@@ -31,7 +31,7 @@ def rms_norm(x, w, eps):
 
 def short_conv(u, w):
     """Causal convolution over time on each channel: u [T, C], w [C, taps];
-    y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the start."""
+    y_t = sum_j w[:, j] u_(t - taps + 1 + j), where u is zero at negative times."""
     T, C = u.shape
     taps = w.shape[1]
     padded = torch.cat([u.new_zeros(taps - 1, C), u], 0)

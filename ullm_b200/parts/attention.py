@@ -64,7 +64,7 @@ class PagedAttention(Mixer):
         c tanh(score / c) after the scale.  `talking_heads`: the softmax weights are mixed across heads by the
         matrix `talk` [heads, heads], w'_h = sum_g talk[h, g] w_g, and head h applies w'_h to the values of its
         own kv head.  `value_mix`: "first": this execution leaves its values of the step's tokens for later ones;
-        "mix": v <- (1 - lambda) v + lambda v_first with the scalar `vmix` (the mixed values are cached); both kinds
+        "mix": v <- (1 - lambda) v + lambda v_first with the scalar `vmix` (what goes to the cache is the blend); both kinds
         declare the scalar.  `unit_norm_after_rotation`: q and k are divided by their root mean square over the
         head (eps `norm_eps`, no weight) behind the rotation.  A position of kind `rope_computed` (angles computed
         in the kernel, optional frequency scaling) also takes this path."""
