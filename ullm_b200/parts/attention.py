@@ -57,13 +57,14 @@ class PagedAttention(Mixer):
         (`ScheduleEntry.cache_of`) with queries, mask and scale of its own.  `names`: the checkpoint's names of
         q, k, v, o, q_norm, k_norm behind the mixer's prefix (defaults: `q_proj.weight`, ..., `q_norm.`).
 
-        Further options, all served by the general kernels (csrc/attention_prep.cu, csrc/attention_generic.cu) in
-        prompt and decode steps alike.  `conv_taps` > 0: a causal convolution over time of that many taps on every
-        channel of q, k and v, directly behind the projection (filters `q_conv`, `k_conv`, `v_conv` [channels,
-        taps]); the last taps - 1 projected rows of a request are per-request state.  `score_cap` c: score <-
+        Further options, all on the general path (csrc/attention_prep.cu, then the tensor-core attention kernels
+        where dtype and head sizes allow, else csrc/attention_generic.cu) in prompt and decode steps alike.
+        `conv_taps` > 0: every channel of q, k and v passes a causal filter over time of that many taps before
+        anything else happens to it (filters `q_conv`, `k_conv`, `v_conv` [channels, taps]); a request keeps its
+        last taps - 1 projected rows as state.  `score_cap` c: score <-
         c tanh(score / c) after the scale.  `talking_heads`: the softmax weights are mixed across heads by the
-        matrix `talk` [heads, heads], w'_h = sum_g talk[h, g] w_g, and head h applies w'_h to the values of its
-        own kv head.  `value_mix`: "first": this execution leaves its values of the step's tokens for later ones;
+        matrix `talk` [heads, heads], w'_h = sum_g talk[h, g] w_g, and the output of head h is w'_h times the
+        values of the kv head that h belongs to.  `value_mix`: "first": this execution leaves its values of the step's tokens for later ones;
         "mix": v <- (1 - lambda) v + lambda v_first with the scalar `vmix` (what goes to the cache is the blend); both kinds
         declare the scalar.  `unit_norm_after_rotation`: q and k are divided by their root mean square over the
         head (eps `norm_eps`, no weight) behind the rotation.  A position of kind `rope_computed` (angles computed
